@@ -550,3 +550,142 @@ class ZepalornConfig:
             o = self.layers[src]
             if (o.kind, o.mixer, o.ff, o.ff_limit) != (layer.kind, layer.mixer, layer.ff, layer.ff_limit):
                 raise ConfigError(f"layers[{i}] runs on the weights of layer {src}, but the rest of its entry differs from that layer's")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Mufotar: a decoder whose config.json lists its layers one by one; in every layer the mixer and the feed-forward read the
+# same normed input and their sum is added to the stream. Mixers: the gated delta rule with a decay per head, or softmax
+# attention beside a selective scan; feed-forwards: a dense gated unit, or routed experts with identity experts and a shared one.
+
+@dataclass(frozen=True)
+class SelectiveScanConfig:
+    """The right half of Mufotar's ``parallel`` mixer: a selective scan with a state per channel and state index."""
+
+    inner: int
+    state: int
+    dt_rank: int
+    conv: int
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "SelectiveScanConfig":
+        c = cls(_pos_int(m, "inner", where), _pos_int(m, "state", where), _pos_int(m, "dt_rank", where), _pos_int(m, "conv", where))
+        if c.state > 256:
+            raise ConfigError(f"config.json: {where}'state' {c.state}: the recurrence is built for state sizes up to 256")
+        if c.conv > 8:
+            raise ConfigError(f"config.json: {where}'conv' must be 1 to 8 taps, got {c.conv}")
+        return c
+
+
+@dataclass(frozen=True)
+class WeightedPairConfig:
+    """Mixer ``parallel`` of Mufotar: attention on the left, a selective scan on the right, summed with a factor each."""
+
+    left: MaskedAttentionConfig
+    right: SelectiveScanConfig
+    left_scale: float
+    right_scale: float
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "WeightedPairConfig":
+        from dataclasses import replace
+
+        left = MaskedAttentionConfig.from_dict(_sub(m, "left", where), where + "left.")
+        if left.mask_size is not None or left.softcap is not None or left.conv:
+            raise ConfigError(f"config.json: {where}left: this attention is causal, without mask, soft cap or convolution")
+        return cls(replace(left, qk_norm=True), SelectiveScanConfig.from_dict(_sub(m, "right", where), where + "right."),
+                   _number(m, "left_scale", where), _number(m, "right_scale", where))
+
+
+@dataclass(frozen=True)
+class RoutedExpertsConfig:
+    """``mlp.kind = "moe"``: ``experts`` gated units of width ``ff`` of which a token uses ``top``; the router has ``identity`` more
+    outputs, which stand for experts that return their input; ``shared_ff`` (or None) is the width of a unit that every token uses."""
+
+    experts: int
+    identity: int
+    top: int
+    ff: int
+    shared_ff: Optional[int]
+
+    @classmethod
+    def from_dict(cls, mlp: Mapping[str, Any], where: str) -> "RoutedExpertsConfig":
+        r = _sub(mlp, "router", where)
+        identity = r.get("identity", 0) or 0
+        if isinstance(identity, bool) or not isinstance(identity, int) or identity < 0:
+            raise ConfigError(f"config.json: {where}router.identity must be a count, got {identity!r}")
+        shared = _opt_sub(mlp, "shared", where)
+        c = cls(_pos_int(r, "experts", where + "router."), identity, _pos_int(r, "top", where + "router."),
+                _pos_int(_sub(mlp, "expert", where), "ff", where + "expert."), _pos_int(shared, "ff", where + "shared.") if shared else None)
+        if c.top > c.experts + c.identity:
+            raise ConfigError(f"config.json: {where}router.top {c.top} is more than the router has outputs")
+        if c.experts + c.identity > 512:
+            raise ConfigError(f"config.json: {where}router: at most 512 outputs are built")
+        return c
+
+
+@dataclass(frozen=True)
+class MufotarLayerConfig:
+    kind: str                       # "delta" or "parallel"
+    mixer: Any
+    mlp: Any                        # None, the width of a dense gated unit, or a RoutedExpertsConfig
+    weights_of: Optional[int] = None  # the layer whose tensors this one runs on (with a cache and state of its own)
+
+
+@dataclass(frozen=True)
+class MufotarConfig:
+    """The whole of a Mufotar config.json: vocabulary, width, norm epsilon, the soft cap on the logits and the list of layers."""
+
+    architecture = "Mufotar"
+
+    vocab: int
+    width: int
+    eps: float
+    logit_softcap: Optional[float]
+    layers: tuple
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "MufotarConfig":
+        if not isinstance(d.get("layers"), (list, tuple)) or not d["layers"]:
+            raise ConfigError("config.json: 'layers' must be a list with at least one layer")
+        layers = []
+        for i, layer in enumerate(d["layers"]):
+            where = f"layers[{i}]."
+            if not isinstance(layer, Mapping):
+                raise ConfigError(f"config.json: layers[{i}] must be an object")
+            kind = layer.get("type")
+            m = _sub(layer, "mixer", where)
+            if kind == "delta":
+                mixer = DeltaConfig.from_dict(m, where + "mixer.")
+            elif kind == "parallel":
+                mixer = WeightedPairConfig.from_dict(m, where + "mixer.")
+            else:
+                raise ConfigError(f"config.json: {where}type {kind!r} is not one of ['delta', 'parallel']")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, Mapping) or mlp.get("kind", "dense") not in ("dense", "moe"):
+                    raise ConfigError(f"config.json: {where}mlp must be null or an object of kind 'dense' or 'moe'")
+                mlp = _pos_int(mlp, "ff", where + "mlp.") if mlp.get("kind", "dense") == "dense" else RoutedExpertsConfig.from_dict(mlp, where + "mlp.")
+            src = layer.get("weights_of")
+            if src is not None and (isinstance(src, bool) or not isinstance(src, int) or src < 0):
+                raise ConfigError(f"config.json: {where}'weights_of' must be a layer index, got {src!r}")
+            layers.append(MufotarLayerConfig(kind, mixer, mlp, src))
+        cap = d.get("logit_softcap")
+        cfg = cls(_pos_int(d, "vocab", ""), _pos_int(d, "width", ""), _number(_sub(d, "norm", ""), "eps", "norm."),
+                  _number(d, "logit_softcap", "") if cap is not None else None, tuple(layers))
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if not self.eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.eps}")
+        if self.logit_softcap is not None and not self.logit_softcap > 0:
+            raise ConfigError(f"logit_softcap must be positive, got {self.logit_softcap}")
+        for i, layer in enumerate(self.layers):
+            src = layer.weights_of
+            if src is None:
+                continue
+            if src == i or src >= len(self.layers) or self.layers[src].weights_of is not None:
+                raise ConfigError(f"layers[{i}].weights_of {src} must name another layer, one with tensors of its own")
+            o = self.layers[src]
+            if (o.kind, o.mixer, o.mlp) != (layer.kind, layer.mixer, layer.mlp):
+                raise ConfigError(f"layers[{i}] runs on the weights of layer {src}, but the rest of its entry differs from that layer's")

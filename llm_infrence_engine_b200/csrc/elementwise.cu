@@ -508,17 +508,18 @@ LLMIE_API int llmie_kv_store(const void* z, int z_stride, int k_col, int v_col, 
 }
 
 // ------------------------------------------------------------------------------------------------
-// out = act(in), elementwise in 32-bit. kind 0: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// out = act(in), elementwise in 32-bit. kind 0: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)));
+// kind 1: a soft cap, param * tanh(z / param).
 // With `clear_in` the input is set to zero after it was read (a float32 accumulation buffer of a split-K product).
 template <typename TI, typename TO>
-__global__ void act_kernel(TI* __restrict__ in, TO* __restrict__ out, long long total, int kind, int clear_in) {
+__global__ void act_kernel(TI* __restrict__ in, TO* __restrict__ out, long long total, int kind, int clear_in, float param) {
     pdl_trigger();
     pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const float z = to_f32(in[i]);
     if (clear_in) in[i] = from_f32<TI>(0.f);
-    const float y = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    const float y = kind == 1 ? param * tanhf(z / param) : 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     out[i] = from_f32<TO>(y);
 }
 
@@ -549,15 +550,15 @@ __global__ void __launch_bounds__(256) act_bf16x8_kernel(const bf16* __restrict_
     *reinterpret_cast<uint4*>(out + i * 8) = packed;
 }
 
-LLMIE_API int llmie_act(void* in, void* out, long long total, int kind, int clear_in, int in_dtype, int out_dtype, cudaStream_t s) {
+LLMIE_API int llmie_act(void* in, void* out, long long total, int kind, int clear_in, float param, int in_dtype, int out_dtype, cudaStream_t s) {
     if (total <= 0) return 0;
-    if (kind != 0) return LLMIE_ERR_BAD_ARGUMENT;
-    if (in_dtype == DT_BF16 && out_dtype == DT_BF16 && !clear_in && total % 8 == 0 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0))
+    if (kind < 0 || kind > 1 || (kind == 1 && !(param > 0.f))) return LLMIE_ERR_BAD_ARGUMENT;
+    if (kind == 0 && in_dtype == DT_BF16 && out_dtype == DT_BF16 && !clear_in && total % 8 == 0 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0))
         return launch_kernel(act_bf16x8_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, s, (const bf16*)in, (bf16*)out, total / 8);
     const dim3 grid((unsigned)((total + 255) / 256));
-    if (in_dtype == DT_F32 && out_dtype == DT_F32) return launch_kernel(act_kernel<float, float>, grid, dim3(256), 0, s, (float*)in, (float*)out, total, kind, clear_in);
-    if (in_dtype == DT_F32 && out_dtype == DT_BF16) return launch_kernel(act_kernel<float, bf16>, grid, dim3(256), 0, s, (float*)in, (bf16*)out, total, kind, clear_in);
-    if (in_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_kernel(act_kernel<bf16, bf16>, grid, dim3(256), 0, s, (bf16*)in, (bf16*)out, total, kind, clear_in);
+    if (in_dtype == DT_F32 && out_dtype == DT_F32) return launch_kernel(act_kernel<float, float>, grid, dim3(256), 0, s, (float*)in, (float*)out, total, kind, clear_in, param);
+    if (in_dtype == DT_F32 && out_dtype == DT_BF16) return launch_kernel(act_kernel<float, bf16>, grid, dim3(256), 0, s, (float*)in, (bf16*)out, total, kind, clear_in, param);
+    if (in_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_kernel(act_kernel<bf16, bf16>, grid, dim3(256), 0, s, (bf16*)in, (bf16*)out, total, kind, clear_in, param);
     return LLMIE_ERR_BAD_ARGUMENT;
 }
 
@@ -565,6 +566,7 @@ LLMIE_API int llmie_act(void* in, void* out, long long total, int kind, int clea
 // A gated unit with bounded halves: for a fused gate/up projection [rows, 2 I] (gate first),
 //   g = min(gate, limit);  u = clamp(up, -limit, limit);  out = g * sigmoid(alpha * g) * (u + shift)
 // in 32-bit; `clear_in` zeroes what was read (a float32 accumulation buffer of a split-K product). grid = (rows, column blocks).
+// limit < 0 asks for another unit instead: out = gelu_tanh(gate) * up with gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
 template <typename TI, typename TO>
 __global__ void glu_clamped_kernel(TI* __restrict__ gu, TO* __restrict__ out, int I, int clear_in, float limit, float alpha, float shift) {
     pdl_trigger();
@@ -574,6 +576,10 @@ __global__ void glu_clamped_kernel(TI* __restrict__ gu, TO* __restrict__ out, in
     TI* row = gu + (size_t)blockIdx.x * 2 * I;
     float g = to_f32(row[i]), u = to_f32(row[I + i]);
     if (clear_in) { row[i] = from_f32<TI>(0.f); row[I + i] = from_f32<TI>(0.f); }
+    if (limit < 0.f) {
+        out[(size_t)blockIdx.x * I + i] = from_f32<TO>(0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u);
+        return;
+    }
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     out[(size_t)blockIdx.x * I + i] = from_f32<TO>(g / (1.0f + expf(-alpha * g)) * (u + shift));

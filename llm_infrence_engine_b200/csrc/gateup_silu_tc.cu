@@ -139,7 +139,11 @@ __global__ void __launch_bounds__(THREADS) gateup_silu_tc_kernel(const __grid_co
                 for (int j = 0; j < 8; ++j) {
                     const float g0 = __uint_as_float(gv[2 * j]), g1 = __uint_as_float(gv[2 * j + 1]);
                     float u0 = __uint_as_float(uv[2 * j]), u1 = __uint_as_float(uv[2 * j + 1]), a, b;
-                    if (limit > 0.f) {   // the clamped unit: min(g, limit) * sigmoid(alpha g) * (clamp(u) + shift)
+                    if (limit < 0.f) {   // the GELU unit (tanh form, tanh(t) = 1 - 2 / (exp(2t) + 1)): 0.5 g (1 + tanh(c (g + 0.044715 g^3))) * u
+                        const float t0 = 0.7978845608028654f * (g0 + 0.044715f * g0 * g0 * g0), t1 = 0.7978845608028654f * (g1 + 0.044715f * g1 * g1 * g1);
+                        a = g0 * (1.0f - __fdividef(1.0f, __expf(2.0f * t0) + 1.0f)) * u0;
+                        b = g1 * (1.0f - __fdividef(1.0f, __expf(2.0f * t1) + 1.0f)) * u1;
+                    } else if (limit > 0.f) {   // the clamped unit: min(g, limit) * sigmoid(alpha g) * (clamp(u) + shift)
                         const float c0 = fminf(g0, limit), c1 = fminf(g1, limit);
                         u0 = fminf(fmaxf(u0, -limit), limit) + shift;
                         u1 = fminf(fmaxf(u1, -limit), limit) + shift;
@@ -216,7 +220,8 @@ int launch_gateup(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, 
 
 // x [M, K] and w [2 I, K] bfloat16 row-major (K and I multiples of 8, bases 16-byte aligned), out bfloat16 [M, I].
 // num_blocks: the persistent grid (the number of multiprocessors; fewer if there are fewer tiles).
-// limit > 0: the epilogue is min(g, limit) * sigmoid(alpha g) * (clamp(u, -limit, limit) + shift); limit <= 0: silu(g) * u.
+// limit > 0: the epilogue is min(g, limit) * sigmoid(alpha g) * (clamp(u, -limit, limit) + shift); limit == 0: silu(g) * u;
+// limit < 0: gelu_tanh(g) * u.
 LLMIE_API int llmie_gateup_glu_tc(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag,
                                    float limit, float alpha, float shift,
                                    cudaStream_t s) {

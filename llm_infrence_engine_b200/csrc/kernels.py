@@ -104,7 +104,9 @@ class CudaKernels:
                    "llmie_kv_store", "llmie_act", "llmie_paged_attention_ext_f32", "llmie_paged_attention_ext_bf16", "llmie_paged_attention_ext_mma",
                    "llmie_attention_ext_mma_fits", "llmie_paged_attention_ext_fa", "llmie_attention_ext_fa_fits",
                    "llmie_layernorm", "llmie_group_rmsnorm_gate", "llmie_dual_rmsnorm_mix", "llmie_glu_clamped", "llmie_qk_norm_rope_store",
-                   "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan", "llmie_zero_fresh_states"):
+                   "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan", "llmie_zero_fresh_states",
+                   "llmie_selective_scan", "llmie_weighted_pair", "llmie_moe_route", "llmie_moe_sort", "llmie_moe_gemm", "llmie_moe_combine",
+                   "llmie_moe_tile_rows"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = self._gate_up_glu_pair = None
@@ -747,7 +749,7 @@ class CudaKernels:
         return self.paged_attention(qkv, k_pool, v_pool, block_table, token_seq, positions, num_heads, num_kv_heads, head_dim, page_size,
                                     scale, window, max_context, batch=batch)
 
-    def gate_up_act(self, x, w_gate_up, out_dtype=None, glu=None):
+    def gate_up_act(self, x, w_gate_up, out_dtype=None, glu=None, activation="silu"):
         """``silu(x Wg^T) * (x Wu^T)`` for the fused matrix ``w_gate_up`` ``[2 I, K]`` (gate rows first). Prompt portions in
         bfloat16 take one tcgen05 kernel whose epilogue is the activation (the float32 sums stay in tensor memory; nothing of
         width 2 I is written); everything else is the product followed by ``silu_mul``. ``glu = (limit, alpha, shift)`` asks for
@@ -756,6 +758,10 @@ class CudaKernels:
         limit, alpha, shift = (float(v) for v in glu) if glu is not None else (0.0, 1.0, 0.0)
         if glu is not None and not limit > 0:
             raise KernelError("gate_up_act: the clamped unit needs a positive limit")
+        if activation not in ("silu", "gelu_tanh") or (glu is not None and activation != "silu"):
+            raise KernelError(f"gate_up_act: activation '{activation}' is not built")
+        if activation == "gelu_tanh":   # ``gelu_tanh(gate) * up``: the kernels of the clamped unit take it as a negative limit
+            glu, limit, alpha, shift = (-1.0, 1.0, 0.0), -1.0, 1.0, 0.0
         M, K_ = x.shape
         if (self.use_tc_gate_up and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and M > self.tc_max_rows and K_ % 8 == 0
                 and w_gate_up.dim() == 2 and w_gate_up.shape[0] % 16 == 0 and w_gate_up.shape[1] == K_ and x.is_contiguous()
@@ -903,8 +909,17 @@ class CudaKernels:
         z = self.linear(x, w, transient=True)
         clear = self._is_transient(z)
         out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
-        self._check(self.lib.llmie_act(_ptr(z), _ptr(out), ctypes.c_longlong(z.numel()), 0, int(clear), self._dt(z, "z"), _DT[out_dtype],
-                                       self._stream()), "act")
+        self._check(self.lib.llmie_act(_ptr(z), _ptr(out), ctypes.c_longlong(z.numel()), 0, int(clear), ctypes.c_float(0.0), self._dt(z, "z"),
+                                       _DT[out_dtype], self._stream()), "act")
+        return out
+
+    def softcap(self, x, cap: float):
+        """``cap * tanh(x / cap)`` of a float32 tensor, element by element."""
+        self._need(x, "x", torch.float32)
+        if not cap > 0:
+            raise KernelError("softcap: the cap must be positive")
+        out = torch.empty_like(x)
+        self._check(self.lib.llmie_act(_ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), 1, 0, ctypes.c_float(cap), 0, 0, self._stream()), "softcap")
         return out
 
     # ------------------------------------------------------------------ attention with extras
@@ -1039,7 +1054,7 @@ class CudaKernels:
         return out
 
     # ------------------------------------------------------------------ layer norm before and after a sublayer
-    def _layernorm(self, x, y, w_post, w_pre, eps, rows, out_dtype, what):
+    def _layernorm(self, x, y, w_post, w_pre, eps, rows, out_dtype, what, b_pre=None):
         self._need(x, "residual", torch.float32, 2)
         N, H = x.shape
         clear = False
@@ -1064,6 +1079,10 @@ class CudaKernels:
             self._need(w_pre, "weight", torch.float32, 1)
             if w_pre.shape[0] != H:
                 raise KernelError(f"{what}: weight has {w_pre.shape[0]} elements, rows have {H}")
+            if b_pre is not None:
+                self._need(b_pre, "bias", torch.float32, 1)
+                if b_pre.shape[0] != H:
+                    raise KernelError(f"{what}: bias has {b_pre.shape[0]} elements, rows have {H}")
             out = torch.empty((n_out, H), dtype=out_dtype, device=x.device)
             out_dt = _DT[out_dtype]
             if y is None:
@@ -1072,15 +1091,15 @@ class CudaKernels:
                 raise KernelError(f"{what}: a rounded result cannot feed a float32 norm")
         elif y is None:
             return None
-        self._check(self.lib.llmie_layernorm(_ptr(x), _ptr(y), y_dt, _ptr(w_post), int(clear), _ptr(w_pre), _ptr(out), out_dt, _ptr(rows), n_out, H,
+        self._check(self.lib.llmie_layernorm(_ptr(x), _ptr(y), y_dt, _ptr(w_post), int(clear), _ptr(w_pre), _ptr(b_pre if w_pre is not None else None), _ptr(out), out_dt, _ptr(rows), n_out, H,
                                              ctypes.c_float(eps), self._stream()), what)
         if clear and rows is not None:
             y.zero_()   # only the chosen rows were read and cleared; the buffer must be zero for its next user
             self.launches += 1
         return out
 
-    def layernorm(self, residual, weight, eps, out_dtype, rows=None):
-        """``(x - mean) / sqrt(var + eps) * weight`` of the stream's rows (or of ``rows``), in ``out_dtype``. A sublayer's result
+    def layernorm(self, residual, weight, eps, out_dtype, rows=None, bias=None):
+        """``(x - mean) / sqrt(var + eps) * weight (+ bias)`` of the stream's rows (or of ``rows``), in ``out_dtype``. A sublayer's result
         whose own layer norm still waits to be added into this stream (``post_norm_add``) is added by the same kernel."""
         y = w_post = None
         if (self._pending_post is not None and self._pending_post[0] is residual and self._pending_post[3] == eps
@@ -1093,7 +1112,7 @@ class CudaKernels:
                 self._pending_post = None
         else:
             self.flush()
-        return self._layernorm(residual, y, w_post, weight, eps, rows, out_dtype, "layernorm")
+        return self._layernorm(residual, y, w_post, weight, eps, rows, out_dtype, "layernorm", b_pre=bias)
 
     def post_norm_add(self, residual, y, weight, eps):
         """``residual += layernorm(y) * weight``: put off until the next ``layernorm`` of the same stream (one pass does both)
@@ -1101,10 +1120,13 @@ class CudaKernels:
         y = self.take_result(y)
         self._pending_post = (residual, y, weight, float(eps))
 
-    def group_rmsnorm_gate(self, x, gate, gate_col, weight, group_size, eps, gate_first, out_dtype):
+    def group_rmsnorm_gate(self, x, gate, gate_col, weight, group_size, eps, gate_first, out_dtype, gate_act="sigmoid"):
         """Float32 rows ``x [N, C]`` normed by their root mean square in groups of ``group_size`` channels, with a gate read
         from columns ``gate_col ..`` of ``gate``: ``gate_first`` multiplies by ``silu(gate)`` before the norm, otherwise by
-        ``sigmoid(gate)`` after it. ``weight`` has one entry per channel, or one per channel of a group (shared by all groups)."""
+        ``sigmoid(gate)`` (or, with ``gate_act="silu"``, by ``silu(gate)``) after it. ``weight`` has one entry per channel, or one
+        per channel of a group (shared by all groups)."""
+        if gate_act not in ("sigmoid", "silu") or (gate_first and gate_act != "sigmoid"):
+            raise KernelError("group_rmsnorm_gate: the gate after the norm is 'sigmoid' or 'silu'; before the norm it is always silu")
         self._need(x, "x", torch.float32, 2)
         N, C = x.shape
         self._need(weight, "weight", torch.float32, 1)
@@ -1115,7 +1137,7 @@ class CudaKernels:
         out = torch.empty((N, C), dtype=out_dtype, device=x.device)
         self._check(self.lib.llmie_group_rmsnorm_gate(_ptr(x), ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.stride(0),
                                                       self._dt(gate, "gate"), _ptr(weight), weight.shape[0], _ptr(out), _DT[out_dtype], N, C,
-                                                      group_size, ctypes.c_float(eps), 0 if gate_first else 1, self._stream()), "group_rmsnorm_gate")
+                                                      group_size, ctypes.c_float(eps), 0 if gate_first else (2 if gate_act == "silu" else 1), self._stream()), "group_rmsnorm_gate")
         return out
 
     def dual_rmsnorm_mix(self, a, b, weight_a, weight_b, eps, coef, add_to):
@@ -1134,9 +1156,23 @@ class CudaKernels:
                     "dual_rmsnorm_mix")
         self._unfresh(add_to)
 
+    def weighted_pair(self, a, b, coef_a, coef_b, add_to):
+        """``add_to += coef_a * a + coef_b * b`` (``add_to`` float32): two sublayer results of one input, each with its factor."""
+        self.flush()
+        self._need(add_to, "add_to", torch.float32, 2)
+        for name, t in (("a", a), ("b", b)):
+            self._need(t, name, None, 2)
+            if tuple(t.shape) != tuple(add_to.shape):
+                raise KernelError(f"weighted_pair: {name} is {list(t.shape)}, the target is {list(add_to.shape)}")
+        self._check(self.lib.llmie_weighted_pair(_ptr(a), self._dt(a, "a"), _ptr(b), self._dt(b, "b"), ctypes.c_float(coef_a), ctypes.c_float(coef_b),
+                                                 _ptr(add_to), ctypes.c_longlong(add_to.numel()), int(self._clears(a)), int(self._clears(b)),
+                                                 self._stream()), "weighted_pair")
+        self._unfresh(add_to)
+
     def glu_clamped(self, gu, limit, alpha, shift, out_dtype=None):
         """``g * sigmoid(alpha g) * (u + shift)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` of a fused gate/up
-        projection ``[rows, 2 I]`` (gate first); a transient float32 input is consumed and cleared."""
+        projection ``[rows, 2 I]`` (gate first); a transient float32 input is consumed and cleared. A negative ``limit`` asks for
+        ``gelu_tanh(gate) * up`` instead."""
         self._need(gu, "gate_up", None, 2)
         if gu.shape[1] % 2:
             raise KernelError("glu_clamped: the row must hold gate and up halves of equal width")
@@ -1204,17 +1240,22 @@ class CudaKernels:
                     "causal_conv")
         return out
 
-    def delta_rule(self, qkv, num_heads, num_kv_heads, head_dim, v_head_dim, a, b, b_col, A_log, dt_bias, state, batch, unit_eps=1e-6):
+    def delta_rule(self, qkv, num_heads, num_kv_heads, head_dim, v_head_dim, a, b, b_col, A_log, dt_bias, state, batch, unit_eps=1e-6,
+                   decay_per_head=False):
         """The gated delta rule with a decay per key channel over the rows of each request, from ``state [slots, heads, v_head_dim, head_dim]``
         (a head's ``S [head_dim, v_head_dim]`` kept column by column):
         ``qkv = [q: kv_heads x head_dim | k: the same | v: heads x v_head_dim]`` (after convolution and activation), ``a [N, heads * head_dim]``
-        the decay's logits, ``b`` (columns from ``b_col``) the logits of beta. Returns float32 ``[N, heads * v_head_dim]``."""
+        the decay's logits, ``b`` (columns from ``b_col``) the logits of beta. ``decay_per_head``: one decay per head, ``a [N, heads]``
+        and ``dt_bias [heads]``. Returns float32 ``[N, heads * v_head_dim]``."""
         self._need(qkv, "qkv", None, 2)
         self._need(state, "state", torch.float32, 4)
         N = qkv.shape[0]
         H, G, D, DV = num_heads, num_kv_heads, head_dim, v_head_dim
-        if a.dim() != 2 or a.stride(1) != 1 or a.dtype != qkv.dtype or a.shape != (N, H * D) or not a.is_cuda:
-            raise KernelError("delta_rule: the decay's logits must be [rows, heads * head_dim] of the same type (they may be columns of wider rows)")
+        DA = 1 if decay_per_head else D
+        if a.dim() != 2 or a.stride(1) != 1 or a.dtype != qkv.dtype or a.shape != (N, H * DA) or not a.is_cuda:
+            raise KernelError("delta_rule: the decay's logits must be [rows, heads * head_dim] (or [rows, heads]) of the same type (they may be columns of wider rows)")
+        if dt_bias.shape[0] != H * DA:
+            raise KernelError("delta_rule: dt_bias needs one entry per decay")
         if qkv.shape[1] < 2 * G * D + H * DV or H % G or D > 256:
             raise KernelError("delta_rule: the rows do not fit the head sizes (head_dim at most 256)")
         if b.dim() != 2 or b.stride(1) != 1 or b.dtype != qkv.dtype or b_col + H > b.shape[1]:
@@ -1224,22 +1265,22 @@ class CudaKernels:
         self._need(A_log, "A_log", torch.float32, 1)
         self._need(dt_bias, "dt_bias", torch.float32, 1)
         dev = qkv.device
-        work = torch.empty((N, 2 * G * D + G + H * D + H), dtype=torch.float32, device=dev)
+        work = torch.empty((N, 2 * G * D + G + H * DA + H), dtype=torch.float32, device=dev)
         flat = work.view(-1)
         o = 0
         pieces = []
-        for n in (N * G * D, N * G * D, N * H * D, N * G, N * H):   # (rows of head_dim floats first: they start on 16-byte boundaries)
+        for n in (N * G * D, N * G * D, N * H * DA, N * G, N * H):   # (rows of head_dim floats first: they start on 16-byte boundaries)
             pieces.append(flat[o:o + n])
             o += n
         qn, kn, decay, kq, beta = pieces
         dt = self._dt(qkv, "qkv")
         self._check(self.lib.llmie_delta_prepare(_ptr(qkv), qkv.shape[1], 0, G * D, _ptr(a), a.stride(0), ctypes.c_void_p(b.data_ptr() + b_col * b.element_size()),
                                                  b.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(qn), _ptr(kn), _ptr(kq), _ptr(decay), _ptr(beta), N, H, G, D,
-                                                 ctypes.c_float(D ** -0.5), ctypes.c_float(unit_eps), dt, self._stream()), "delta_rule (prepare)")
+                                                 ctypes.c_float(D ** -0.5), ctypes.c_float(unit_eps), int(bool(decay_per_head)), dt, self._stream()), "delta_rule (prepare)")
         out = torch.empty((N, H * DV), dtype=torch.float32, device=dev)
         self._check(self.lib.llmie_delta_scan(_ptr(qkv), qkv.shape[1], 2 * G * D, _ptr(qn), _ptr(kn), _ptr(kq), _ptr(decay), _ptr(beta), _ptr(state),
-                                              _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots), _ptr(out), H, G, D, DV, batch.num_seqs, batch.max_seq_len, dt,
-                                              self._stream()), "delta_rule (scan)")
+                                              _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots), _ptr(out), H, G, D, DV, batch.num_seqs, batch.max_seq_len,
+                                              int(bool(decay_per_head)), dt, self._stream()), "delta_rule (scan)")
         return out
 
     def ssm_scan(self, xbc, num_heads, groups, state_size, v_head_dim, dt, dt_col, A_log, dt_bias, skip, state, batch):
@@ -1264,6 +1305,88 @@ class CudaKernels:
                                             dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(skip), _ptr(state), _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots),
                                             _ptr(out), H, G, NS, DV, batch.num_seqs, batch.max_seq_len, self._dt(xbc, "xbc"), self._stream()), "ssm_scan")
         return out
+
+    def selective_scan(self, x, dt, bc, b_col, c_col, z, z_col, A_log, dt_bias, skip, state, batch):
+        """The selective scan with a state per channel and state index over the rows of each request, from ``state [slots, channels,
+        state_size]``: ``x [N, channels]`` (after convolution and activation), ``dt [N, channels]`` the step sizes' logits (``dt_bias`` is
+        added and softplus taken here), ``bc`` rows that hold B from column ``b_col`` and C from ``c_col``, ``z`` (columns from ``z_col``)
+        the gate; ``A_log [channels, state_size]``. Returns ``(y + skip x) silu(z)`` as ``[N, channels]`` in x's type."""
+        self._need(x, "x", None, 2)
+        self._need(dt, "dt", x.dtype, 2)
+        self._need(state, "state", torch.float32, 3)
+        self._need(A_log, "A_log", torch.float32, 2)
+        N, C = x.shape
+        NS = A_log.shape[1]
+        if tuple(dt.shape) != (N, C) or A_log.shape[0] != C or NS > 256:
+            raise KernelError("selective_scan: dt and A_log must match the channels (state size at most 256)")
+        for name, t in (("dt_bias", dt_bias), ("skip", skip)):
+            self._need(t, name, torch.float32, 1)
+            if t.shape[0] != C:
+                raise KernelError(f"selective_scan: {name} needs one entry per channel")
+        for name, t, cols in (("bc", bc, max(b_col, c_col) + NS), ("z", z, z_col + C)):
+            if t.dim() != 2 or t.stride(1) != 1 or t.dtype != x.dtype or t.shape[0] != N or cols > t.shape[1] or not t.is_cuda:
+                raise KernelError(f"selective_scan: {name} must be rows of the same type that hold the columns asked for")
+        if tuple(state.shape[1:]) != (C, NS):
+            raise KernelError(f"selective_scan: state is {list(state.shape)}, expected [slots, {C}, {NS}]")
+        out = torch.empty((N, C), dtype=x.dtype, device=x.device)
+        self._check(self.lib.llmie_selective_scan(_ptr(x), x.stride(0), _ptr(dt), dt.stride(0), _ptr(bc), bc.stride(0), int(b_col), int(c_col),
+                                                  ctypes.c_void_p(z.data_ptr() + z_col * z.element_size()), z.stride(0), _ptr(A_log), _ptr(dt_bias),
+                                                  _ptr(skip), _ptr(state), _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots), _ptr(out), C, NS,
+                                                  batch.num_seqs, batch.max_seq_len, self._dt(x, "x"), self._stream()), "selective_scan")
+        return out
+
+    # ------------------------------------------------------------------ routed experts
+    def moe_route(self, logits, correction, top: int):
+        """From float32 router logits ``[N, outputs]``: ``s = softmax(logits)``; the ``top`` outputs with the largest ``s + correction``
+        (``correction`` may be None); returns ``(ids [N, top] int32, weights [N, top] float32)`` with the weights ``s / (sum of the chosen s + 1e-20)``."""
+        self._need(logits, "logits", torch.float32, 2)
+        N, total = logits.shape
+        if correction is not None:
+            self._need(correction, "correction", torch.float32, 1)
+            if correction.shape[0] != total:
+                raise KernelError("moe_route: the correction needs one entry per router output")
+        if not 1 <= top <= total or total > 512:
+            raise KernelError(f"moe_route: {top} of {total} router outputs cannot be chosen (at most 512 outputs)")
+        ids = torch.empty((N, top), dtype=torch.int32, device=logits.device)
+        weights = torch.empty((N, top), dtype=torch.float32, device=logits.device)
+        self._check(self.lib.llmie_moe_route(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), N, total, top, self._stream()), "moe_route")
+        return ids, weights
+
+    def moe_experts(self, h, ids, weights, w_gate_up, w_down, add_to):
+        """``add_to[t] += sum_k weights[t, k] * expert_(ids[t, k])(h[t])``: expert ``e < E`` is ``down_e(silu(gate_e x) * (up_e x))`` with
+        ``w_gate_up [E, 2 F, K]`` (an expert's gate rows, then its up rows) and ``w_down [E, K, F]``; an id from ``E`` on is an identity
+        expert whose output is ``h[t]`` itself. The (token, choice) pairs are sorted by expert on the device and every expert's rows go
+        through its matrices as tiles of one grouped product."""
+        self.flush()
+        self._need(h, "h", None, 2)
+        self._need(add_to, "add_to", torch.float32, 2)
+        self._need(ids, "ids", torch.int32, 2)
+        self._need(weights, "weights", torch.float32, 2)
+        self._need(w_gate_up, "w_gate_up", h.dtype, 3)
+        self._need(w_down, "w_down", h.dtype, 3)
+        N, K = h.shape
+        top = ids.shape[1]
+        E, F2, _ = w_gate_up.shape
+        F = F2 // 2
+        if tuple(w_gate_up.shape) != (E, 2 * F, K) or tuple(w_down.shape) != (E, K, F) or tuple(add_to.shape) != (N, K) or tuple(weights.shape) != (N, top) or ids.shape[0] != N:
+            raise KernelError("moe_experts: the matrices, the choices and the rows do not fit each other")
+        dev = h.device
+        pairs = N * top
+        tile_rows = self.lib.llmie_moe_tile_rows()
+        max_tiles = -(-pairs // tile_rows) + E
+        book = torch.empty((E + 1 + 2 * pairs + 1 + 2 * max_tiles,), dtype=torch.int32, device=dev)
+        offsets, perm, place_of, tiles = book[:E + 1], book[E + 1:E + 1 + pairs], book[E + 1 + pairs:E + 1 + 2 * pairs], book[E + 1 + 2 * pairs:]
+        self._check(self.lib.llmie_moe_sort(_ptr(ids), pairs, E, _ptr(offsets), _ptr(perm), _ptr(place_of), _ptr(tiles), max_tiles, self._stream()), "moe_experts (sort)")
+        dt = self._dt(h, "h")
+        act = torch.empty((pairs, F), dtype=h.dtype, device=dev)
+        self._check(self.lib.llmie_moe_gemm(_ptr(h), _ptr(perm), top, _ptr(w_gate_up), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(act), F, K, 1, dt,
+                                            self._stream()), "moe_experts (gate and up)")
+        y = torch.empty((pairs, K), dtype=torch.float32, device=dev)
+        self._check(self.lib.llmie_moe_gemm(_ptr(act), _ptr(None), 1, _ptr(w_down), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(y), K, F, 0, dt,
+                                            self._stream()), "moe_experts (down)")
+        self._check(self.lib.llmie_moe_combine(_ptr(add_to), _ptr(y), _ptr(h), _ptr(place_of), _ptr(weights), N, top, K, dt, self._stream()),
+                    "moe_experts (sum)")
+        self._unfresh(add_to)
 
     # ------------------------------------------------------------------ latent attention
     def latent_prepare(self, z, q_rank, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, eps, cos, sin, slot_mapping, kc_pool, page_size, write=True):

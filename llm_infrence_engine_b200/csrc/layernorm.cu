@@ -1,4 +1,4 @@
-// Layer norm with a weight and no bias, for blocks that norm a sublayer's input AND its result:
+// Layer norm with a weight (and, for the norm of a sublayer's input, an optional bias), for blocks that norm a sublayer's input AND its result:
 //   x <- x + LN_post(y);  h = LN_pre(x)
 // One kernel does either half or both, one block per row, the row in shared memory between the passes. Mean, variance
 // (the mean of the squared deviations, taken in a second pass about the finished mean) and the scaling are 32-bit. Also here: the root-mean-square
@@ -14,7 +14,7 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 // rows == nullptr: r = blockIdx.x and the updated x is stored; rows != nullptr: r = rows[blockIdx.x], nothing of x is stored.
 // y (of type TY, or null): the sublayer's result whose layer norm (weight w_post) is added to x first; with clear_y the row of
 // y is set to zero behind the read (it is then a float buffer that the next sublayer adds into).
-// w_pre (or null): out[blockIdx.x] = LN(x) * w_pre in type TO.
+// w_pre (or null): out[blockIdx.x] = LN(x) * w_pre (+ b_pre, if given) in type TO.
 // Mean and reciprocal standard deviation of the H floats of buf, in two passes (the squared deviations are taken about the
 // finished mean); every thread gets both. A thread reads the entries it wrote itself, so no barrier is needed before.
 template <int VEC>
@@ -39,7 +39,8 @@ __device__ __forceinline__ void row_stats(const float* buf, int H, int step, flo
 
 template <typename TY, typename TO, int VEC>
 __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, const float* __restrict__ w_post, int clear_y,
-                                 const float* __restrict__ w_pre, TO* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+                                 const float* __restrict__ w_pre, const float* __restrict__ b_pre, TO* __restrict__ out,
+                                 const int* __restrict__ rows, int H, float eps) {
     extern __shared__ __align__(16) float ln_buf[];   // the row of x, the row of y, both weights (H floats each), 100 for the reductions
     float* x_buf = ln_buf;
     float* y_buf = x_buf + H;
@@ -94,13 +95,17 @@ __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, cons
         if constexpr (VEC == 4) { load4(x_buf + i, v); load4(wq_buf + i, w); } else { v[0] = x_buf[i]; w[0] = wq_buf[i]; }
 #pragma unroll
         for (int j = 0; j < VEC; ++j) v[j] = (v[j] - mean) * rstd * w[j];
+        if (b_pre) {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[j] += b_pre[i + j];
+        }
         if constexpr (VEC == 4) store4(o + i, v); else o[i] = from_f32<TO>(v[0]);
     }
 }
 
 template <typename TY, typename TO>
-int launch_layernorm(float* x, void* y, const float* w_post, int clear_y, const float* w_pre, void* out, const int* rows, int n_out,
-                     int H, float eps, cudaStream_t s) {
+int launch_layernorm(float* x, void* y, const float* w_post, int clear_y, const float* w_pre, const float* b_pre, void* out, const int* rows,
+                     int n_out, int H, float eps, cudaStream_t s) {
     const size_t smem = (size_t)(4 * H + 100) * sizeof(float);
     const bool vec = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
                      ((uintptr_t)w_post % 16 == 0) && ((uintptr_t)w_pre % 16 == 0);
@@ -109,15 +114,16 @@ int launch_layernorm(float* x, void* y, const float* w_post, int clear_y, const 
     while (threads < 512 && threads * per * 2 <= H) threads *= 2;
     if (vec) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TY, TO, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return launch_kernel(layernorm_kernel<TY, TO, 4>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, (TO*)out, rows, H, eps);
+        return launch_kernel(layernorm_kernel<TY, TO, 4>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, b_pre, (TO*)out, rows, H, eps);
     }
     if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TY, TO, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_kernel(layernorm_kernel<TY, TO, 1>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, (TO*)out, rows, H, eps);
+    return launch_kernel(layernorm_kernel<TY, TO, 1>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, b_pre, (TO*)out, rows, H, eps);
 }
 
 // Root-mean-square norm over groups of `gs` consecutive channels, with a gate, one block per (row, group):
 //   mode 0: v = x * silu(gate);            out = v / rms(v) * w                     (the gate comes before the norm)
 //   mode 1: out = x / rms(x) * w * sigmoid(gate)                                    (the gate comes after it)
+//   mode 2: out = x / rms(x) * w * silu(gate)
 // w has w_len entries and channel c uses w[c % w_len] (one weight per channel, or one vector shared by all groups).
 template <typename TG, typename TO>
 __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ x, const TG* __restrict__ gate, int gate_stride,
@@ -142,6 +148,7 @@ __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ x, const TG*
         if (mode == 0) v *= z / (1.0f + expf(-z));
         v = v * rstd * w[(c0 + i) % w_len];
         if (mode == 1) v *= sigmoid_f(z);
+        if (mode == 2) v *= z * sigmoid_f(z);
         o[i] = from_f32<TO>(v);
     }
 }
@@ -181,6 +188,7 @@ __global__ void __launch_bounds__(128) group_rmsnorm_gate_warp_kernel(const floa
         if (i < gs) {
             float r = v[k] * rstd * w[(c0 + i) % w_len];
             if (mode == 1) r *= sigmoid_f(z[k]);
+            if (mode == 2) r *= z[k] * sigmoid_f(z[k]);
             o[i] = from_f32<TO>(r);
         }
     }
@@ -213,22 +221,50 @@ __global__ void dual_rmsnorm_mix_kernel(TA* __restrict__ a, TB* __restrict__ b, 
     }
 }
 
+// y[i] += ca * a[i] + cb * b[i]: two sublayer results of one input, each with a factor of its own. The inputs may be float sums or
+// rounded rows of a library product; with clear_a / clear_b an input is set to zero behind the read.
+template <typename TA, typename TB>
+__global__ void weighted_pair_kernel(TA* __restrict__ a, TB* __restrict__ b, float ca, float cb, float* __restrict__ y, long long total,
+                                     int clear_a, int clear_b) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float v = fmaf(ca, to_f32(a[i]), cb * to_f32(b[i]));
+    if (clear_a) a[i] = from_f32<TA>(0.f);
+    if (clear_b) b[i] = from_f32<TB>(0.f);
+    y[i] += v;
+}
+
 }  // namespace
 
-LLMIE_API int llmie_layernorm(float* x, void* y, int y_dtype, const float* w_post, int clear_y, const float* w_pre, void* out,
+LLMIE_API int llmie_weighted_pair(void* a, int a_dtype, void* b, int b_dtype, float ca, float cb, float* y, long long total, int clear_a,
+                                  int clear_b, cudaStream_t s) {
+    if (total <= 0) return 0;
+    const dim3 grid((unsigned)((total + 255) / 256));
+#define LLMIE_PAIR(TA, TB) return launch_kernel(weighted_pair_kernel<TA, TB>, grid, dim3(256), 0, s, (TA*)a, (TB*)b, ca, cb, y, total, clear_a, clear_b)
+    if (a_dtype == DT_F32 && b_dtype == DT_F32) LLMIE_PAIR(float, float);
+    if (a_dtype == DT_F32 && b_dtype == DT_BF16) LLMIE_PAIR(float, bf16);
+    if (a_dtype == DT_BF16 && b_dtype == DT_F32) LLMIE_PAIR(bf16, float);
+    if (a_dtype == DT_BF16 && b_dtype == DT_BF16) LLMIE_PAIR(bf16, bf16);
+#undef LLMIE_PAIR
+    return LLMIE_ERR_BAD_ARGUMENT;
+}
+
+LLMIE_API int llmie_layernorm(float* x, void* y, int y_dtype, const float* w_post, int clear_y, const float* w_pre, const float* b_pre, void* out,
                               int out_dtype, const int* rows, int n_out, int H, float eps, cudaStream_t s) {
     if (n_out <= 0) return 0;
     if (H <= 0 || (size_t)(4 * H + 100) * sizeof(float) > 200 * 1024 || (y && !w_post) || (w_pre && !out)) return LLMIE_ERR_BAD_ARGUMENT;
-    if (y_dtype == DT_F32 && out_dtype == DT_F32) return launch_layernorm<float, float>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
-    if (y_dtype == DT_F32 && out_dtype == DT_BF16) return launch_layernorm<float, bf16>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
-    if (y_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_layernorm<bf16, bf16>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
+    if (y_dtype == DT_F32 && out_dtype == DT_F32) return launch_layernorm<float, float>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, s);
+    if (y_dtype == DT_F32 && out_dtype == DT_BF16) return launch_layernorm<float, bf16>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, s);
+    if (y_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_layernorm<bf16, bf16>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, s);
     return LLMIE_ERR_BAD_ARGUMENT;
 }
 
 LLMIE_API int llmie_group_rmsnorm_gate(const float* x, const void* gate, int gate_stride, int gate_dtype, const float* w, int w_len,
                                        void* out, int out_dtype, int N, int C, int gs, float eps, int mode, cudaStream_t s) {
     if (N <= 0) return 0;
-    if (C <= 0 || gs <= 0 || C % gs || w_len <= 0 || C / gs > 65535 || mode < 0 || mode > 1) return LLMIE_ERR_BAD_ARGUMENT;
+    if (C <= 0 || gs <= 0 || C % gs || w_len <= 0 || C / gs > 65535 || mode < 0 || mode > 2) return LLMIE_ERR_BAD_ARGUMENT;
     int threads = 32;
     while (threads < 256 && threads * 2 <= gs) threads *= 2;
     const dim3 grid(N, C / gs);

@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
 // ------------------------------------------------------------------------------------------------
 // What the delta rule's recurrence reads, made from the projections in one parallel pass. One warp per (token, head):
 //   decay[n, h, d] = exp(-exp(A_log[h]) * softplus(a[n, h, d] + dt_bias[h, d]))
+//   (per_head: one decay per head, decay[n, h] = exp(-exp(A_log[h]) * softplus(a[n, h] + dt_bias[h])))
 //   beta[n, h]     = sigmoid(b[n, h])
 // and, by the first head of every key group g, the unit vectors
 //   qn[n, g, :] = q / sqrt(sum q^2 + unit_eps) * q_scale,   kn[n, g, :] = k / sqrt(sum k^2 + unit_eps),   kq[n, g] = kn . qn
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict_
                                                             const float* __restrict__ dt_bias, float* __restrict__ qn,
                                                             float* __restrict__ kn, float* __restrict__ kq, float* __restrict__ decay,
                                                             float* __restrict__ beta, int N, int H, int G, int D, float q_scale,
-                                                            float unit_eps) {
+                                                            float unit_eps, int per_head) {
     pdl_trigger();
     pdl_wait();
     const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -104,9 +105,13 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict_
     if (item >= N * H) return;
     const int n = item / H, h = item % H;
     const float rate = expf(A_log[h]);
-    for (int d = lane; d < D; d += 32) {
-        const float x = to_f32(a[(size_t)n * a_stride + h * D + d]) + dt_bias[h * D + d];
-        decay[((size_t)n * H + h) * D + d] = expf(-rate * softplus_f(x));
+    if (per_head) {
+        if (lane == 0) decay[(size_t)n * H + h] = expf(-rate * softplus_f(to_f32(a[(size_t)n * a_stride + h]) + dt_bias[h]));
+    } else {
+        for (int d = lane; d < D; d += 32) {
+            const float x = to_f32(a[(size_t)n * a_stride + h * D + d]) + dt_bias[h * D + d];
+            decay[((size_t)n * H + h) * D + d] = expf(-rate * softplus_f(x));
+        }
     }
     if (lane == 0) beta[(size_t)n * H + h] = sigmoid_f(to_f32(bsrc[(size_t)n * b_stride + h]));
     const int per = H / G;
@@ -216,8 +221,9 @@ __device__ __forceinline__ void store_column(const float* S, float* st, int part
 // The gated delta rule. For every token, in order:
 //   S <- decay (.) S (row d by decay[d]);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 // With S' = decay (.) S both products of a token are taken from S' in one pass over the registers: r = S'^T k and S'^T q, and
-// then o = S'^T q + u (k . q), the last factor coming with the token.
-template <typename T, int DMAX, int PARTS>
+// then o = S'^T q + u (k . q), the last factor coming with the token. SCALAR: the decay is one number per token and head
+// (decay [N, H]) and comes with the token's other numbers instead of as a row of D.
+template <typename T, int DMAX, int PARTS, bool SCALAR>
 __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(const T* __restrict__ v, int v_stride, int v_col, const float* __restrict__ qn,
                                                                   const float* __restrict__ kn, const float* __restrict__ kq,
                                                                   const float* __restrict__ decay, const float* __restrict__ beta,
@@ -231,7 +237,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(const T* __res
     float* g_s = q_s + 2 * SCAN_TILE * DMAX;
     float* beta_s = g_s + 2 * SCAN_TILE * DMAX;          // [2][SCAN_TILE]
     float* kq_s = beta_s + 2 * SCAN_TILE;
-    float* v_s = kq_s + 2 * SCAN_TILE;                   // [2][SCAN_TILE][COLS]
+    float* g1_s = kq_s + 2 * SCAN_TILE;                  // [2][SCAN_TILE]: the decay where it is one number per token
+    float* v_s = g1_s + 2 * SCAN_TILE;                   // [2][SCAN_TILE][COLS]
     pdl_wait();
     const int part = threadIdx.x % PARTS;
     const int col = blockIdx.x * COLS + threadIdx.x / PARTS;
@@ -247,18 +254,19 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(const T* __res
         const int count = min(SCAN_TILE, s1 - base);
         fetch_rows<DMAX>(k_s + buf * SCAN_TILE * DMAX, kn + ((size_t)base * G + g) * D, (size_t)G * D, count, D, vec);
         fetch_rows<DMAX>(q_s + buf * SCAN_TILE * DMAX, qn + ((size_t)base * G + g) * D, (size_t)G * D, count, D, vec);
-        fetch_rows<DMAX>(g_s + buf * SCAN_TILE * DMAX, decay + ((size_t)base * H + h) * D, (size_t)H * D, count, D, vec);
+        if constexpr (!SCALAR) fetch_rows<DMAX>(g_s + buf * SCAN_TILE * DMAX, decay + ((size_t)base * H + h) * D, (size_t)H * D, count, D, vec);
     };
     // A tile's numbers per token (beta, k . q) and the block's columns of v: loaded into registers a tile ahead, put into shared
     // memory after the tile's work, so that nobody waits for them. Thread i < SCAN_TILE holds token i's two numbers; the
     // threads from the end backwards hold v, VPT values each.
     constexpr int VPT = (SCAN_TILE * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
-    float pre_beta = 0.f, pre_kq = 0.f, pre_v[VPT];
+    float pre_beta = 0.f, pre_kq = 0.f, pre_g = 1.f, pre_v[VPT];
     auto load_small = [&](int base) {
         const int count = min(SCAN_TILE, s1 - base);
         if (threadIdx.x < count) {
             pre_beta = beta[(size_t)(base + threadIdx.x) * H + h];
             pre_kq = kq[(size_t)(base + threadIdx.x) * G + g];
+            if constexpr (SCALAR) pre_g = decay[(size_t)(base + threadIdx.x) * H + h];
         }
 #pragma unroll
         for (int n = 0; n < VPT; ++n) {
@@ -271,6 +279,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(const T* __res
         if (threadIdx.x < SCAN_TILE) {
             beta_s[buf * SCAN_TILE + threadIdx.x] = pre_beta;
             kq_s[buf * SCAN_TILE + threadIdx.x] = pre_kq;
+            if constexpr (SCALAR) g1_s[buf * SCAN_TILE + threadIdx.x] = pre_g;
         }
 #pragma unroll
         for (int n = 0; n < VPT; ++n) {
@@ -303,11 +312,13 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(const T* __res
         for (int t = 0; t < SCAN_TILE; ++t) {
             if (t < count) {
                 float rk0 = 0.f, rk1 = 0.f, rq0 = 0.f, rq1 = 0.f;
+                float g1 = 1.f;
+                if constexpr (SCALAR) g1 = g1_s[buf * SCAN_TILE + t];
 #pragma unroll
                 for (int i = 0; i < DPL / 4; ++i) {
                     const float4 k4 = *reinterpret_cast<const float4*>(kb + t * DMAX + 4 * PARTS * i);
                     const float4 q4 = *reinterpret_cast<const float4*>(qb + t * DMAX + 4 * PARTS * i);
-                    const float4 g4 = *reinterpret_cast<const float4*>(gb + t * DMAX + 4 * PARTS * i);
+                    const float4 g4 = SCALAR ? make_float4(g1, g1, g1, g1) : *reinterpret_cast<const float4*>(gb + t * DMAX + 4 * PARTS * i);
                     float* s = S + 4 * i;
                     s[0] *= g4.x; s[1] *= g4.y; s[2] *= g4.z; s[3] *= g4.w;
                     rk0 = fmaf(s[0], k4.x, rk0); rk1 = fmaf(s[1], k4.y, rk1); rk0 = fmaf(s[2], k4.z, rk0); rk1 = fmaf(s[3], k4.w, rk1);
@@ -446,6 +457,129 @@ __global__ void __launch_bounds__(SCAN_THREADS) ssm_scan_kernel(const T* __restr
     if (live) store_column<DPL, PARTS>(S, st, part, NS, vec);
 }
 
+// ------------------------------------------------------------------------------------------------
+// The selective scan with a state per channel and state index (the recurrence of Mamba). Per channel c, S[c] is NS numbers; for
+// every token, in order:
+//   dt = softplus(dt_raw[c] + dt_bias[c]);  S[c, n] <- exp(dt A[c, n]) S[c, n] + dt x[c] B[n];  y[c] = sum_n S[c, n] C[n] + D[c] x[c]
+// with A = -exp(A_log) [C, NS], B and C shared by all channels of a token. The result leaves as y * silu(z) in the storage type.
+// The layout is the one above with a channel in the place of a column: PARTS lanes share a channel, each with its entries of S and
+// of A in registers; a block owns SCAN_THREADS / PARTS channels; tiles of SCAN_TILE tokens are loaded into registers a tile ahead.
+template <typename T, int NMAX, int PARTS>
+__global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ dt_raw, int dt_stride,
+                                                                      const T* __restrict__ bc, int bc_stride, int b_col, int c_col,
+                                                                      const T* __restrict__ z, int z_stride, const float* __restrict__ A_log,
+                                                                      const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
+                                                                      float* __restrict__ state, const int* __restrict__ seq_starts,
+                                                                      const int* __restrict__ seq_slots, T* __restrict__ out, int C, int NS) {
+    constexpr int DPL = NMAX / PARTS, COLS = SCAN_THREADS / PARTS;
+    extern __shared__ __align__(16) float scan_smem[];
+    float* b_s = scan_smem;                              // [2][SCAN_TILE][NMAX]
+    float* c_s = b_s + 2 * SCAN_TILE * NMAX;
+    float* x_s = c_s + 2 * SCAN_TILE * NMAX;             // [2][SCAN_TILE][COLS]
+    float* dt_s = x_s + 2 * SCAN_TILE * COLS;
+    float* z_s = dt_s + 2 * SCAN_TILE * COLS;
+    const int part = threadIdx.x % PARTS;
+    const int my_col = threadIdx.x / PARTS;
+    const int col = blockIdx.x * COLS + my_col;
+    const int r = blockIdx.z;
+    const bool live = col < C;
+    const bool vec = (NS & 3) == 0;
+    // the channel's rates and numbers do not depend on the kernel before: fetched before the wait
+    float A[DPL];
+    load_column<DPL, PARTS>(A, A_log + (size_t)(live ? col : 0) * NS, part, NS, live, vec);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) A[i] = -expf(A[i]);
+    const float skip = live ? Dskip[col] : 0.f;
+    pdl_wait();
+    const int s0 = seq_starts[r], s1 = seq_starts[r + 1];
+    float* st = state + ((size_t)seq_slots[r] * C + (live ? col : 0)) * NS;
+    float S[DPL];
+    load_column<DPL, PARTS>(S, st, part, NS, live, vec);
+    constexpr int BPT = (SCAN_TILE * NMAX + SCAN_THREADS - 1) / SCAN_THREADS;
+    constexpr int XPT = (SCAN_TILE * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
+    float pre_b[BPT], pre_c[BPT], pre_x[XPT], pre_dt[XPT], pre_z[XPT];
+    auto load_tile = [&](int base) {
+        const int count = min(SCAN_TILE, s1 - base);
+#pragma unroll
+        for (int n = 0; n < BPT; ++n) {
+            const int i = threadIdx.x + n * SCAN_THREADS;
+            const int t = i / NMAX, d = i % NMAX;
+            const bool in = t < count && d < NS;
+            const size_t row = (size_t)(base + t) * bc_stride;
+            pre_b[n] = in ? to_f32(bc[row + b_col + d]) : 0.f;
+            pre_c[n] = in ? to_f32(bc[row + c_col + d]) : 0.f;
+        }
+#pragma unroll
+        for (int n = 0; n < XPT; ++n) {
+            const int j = threadIdx.x + n * SCAN_THREADS;
+            const int t = j / COLS, c = blockIdx.x * COLS + j % COLS;
+            const bool in = j < count * COLS && c < C;
+            pre_x[n] = in ? to_f32(x[(size_t)(base + t) * x_stride + c]) : 0.f;
+            pre_z[n] = in ? to_f32(z[(size_t)(base + t) * z_stride + c]) : 0.f;
+            pre_dt[n] = in ? softplus_f(to_f32(dt_raw[(size_t)(base + t) * dt_stride + c]) + dt_bias[c]) : 0.f;
+        }
+    };
+    auto store_tile = [&](int buf) {
+#pragma unroll
+        for (int n = 0; n < BPT; ++n) {
+            const int i = threadIdx.x + n * SCAN_THREADS;
+            if (i < SCAN_TILE * NMAX) {
+                b_s[buf * SCAN_TILE * NMAX + i] = pre_b[n];
+                c_s[buf * SCAN_TILE * NMAX + i] = pre_c[n];
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < XPT; ++n) {
+            const int j = threadIdx.x + n * SCAN_THREADS;
+            if (j < SCAN_TILE * COLS) {
+                x_s[buf * SCAN_TILE * COLS + j] = pre_x[n];
+                dt_s[buf * SCAN_TILE * COLS + j] = pre_dt[n];
+                z_s[buf * SCAN_TILE * COLS + j] = pre_z[n];
+            }
+        }
+    };
+    if (s0 < s1) {
+        load_tile(s0);
+        store_tile(0);
+    }
+    int buf = 0;
+    for (int base = s0; base < s1; base += SCAN_TILE, buf ^= 1) {
+        const int count = min(SCAN_TILE, s1 - base);
+        const bool more = base + SCAN_TILE < s1;
+        __syncthreads();                       // this tile is in shared memory; everyone is done with the other stage
+        if (more) load_tile(base + SCAN_TILE);
+        const float* bb = b_s + buf * SCAN_TILE * NMAX + 4 * part;
+        const float* cb = c_s + buf * SCAN_TILE * NMAX + 4 * part;
+#pragma unroll
+        for (int t = 0; t < SCAN_TILE; ++t) {
+            if (t < count) {
+                const float xv = x_s[(buf * SCAN_TILE + t) * COLS + my_col];
+                const float dt = dt_s[(buf * SCAN_TILE + t) * COLS + my_col];
+                const float u = dt * xv;
+                float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPL / 4; ++i) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bb + t * NMAX + 4 * PARTS * i);
+                    const float4 c4 = *reinterpret_cast<const float4*>(cb + t * NMAX + 4 * PARTS * i);
+                    float* sp = S + 4 * i;
+                    const float* ap = A + 4 * i;
+                    sp[0] = fmaf(expf(dt * ap[0]), sp[0], b4.x * u); sp[1] = fmaf(expf(dt * ap[1]), sp[1], b4.y * u);
+                    sp[2] = fmaf(expf(dt * ap[2]), sp[2], b4.z * u); sp[3] = fmaf(expf(dt * ap[3]), sp[3], b4.w * u);
+                    y0 = fmaf(sp[0], c4.x, y0); y1 = fmaf(sp[1], c4.y, y1); y0 = fmaf(sp[2], c4.z, y0); y1 = fmaf(sp[3], c4.w, y1);
+                }
+                const float y = parts_sum<PARTS>(y0 + y1);
+                if (live && part == 0) {
+                    const float zv = z_s[(buf * SCAN_TILE + t) * COLS + my_col];
+                    out[(size_t)(base + t) * C + col] = from_f32<T>(fmaf(skip, xv, y) * silu_f(zv));
+                }
+            }
+        }
+        if (more) store_tile(buf ^ 1);         // (the other stage: nobody reads it before the next barrier)
+    }
+    pdl_trigger();                             // (not before: see the delta rule's kernel)
+    if (live) store_column<DPL, PARTS>(S, st, part, NS, vec);
+}
+
 template <typename T>
 int launch_conv(const T* z, int z_stride, int C, const float* w, const float* bias, float* state, const int* seq_starts,
                 const int* seq_slots, T* out, int out_stride, int taps, int act, int R, int max_rows, cudaStream_t s) {
@@ -454,16 +588,25 @@ int launch_conv(const T* z, int z_stride, int C, const float* w, const float* bi
                          out_stride, taps, act);
 }
 
+template <typename T, int DM, int PARTS, bool SCALAR>
+int launch_delta_scan_one(const T* v, int v_stride, int v_col, const float* qn, const float* kn, const float* kq, const float* decay,
+                          const float* beta, float* state, const int* seq_starts, const int* seq_slots, float* out, int H, int G, int D, int DV,
+                          int R, bool alone, cudaStream_t s) {
+    constexpr int cols = SCAN_THREADS / PARTS;
+    const dim3 grid((DV + cols - 1) / cols, H, R);
+    const size_t smem = sizeof(float) * (2 * SCAN_TILE * (3 * DM + 3 + cols));
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<T, DM, PARTS, SCALAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_kernel_on(alone, delta_scan_kernel<T, DM, PARTS, SCALAR>, grid, dim3(SCAN_THREADS), smem, s, v, v_stride, v_col, qn, kn, kq, decay,
+                            beta, state, seq_starts, seq_slots, out, H, G, D, DV);
+}
+
 template <typename T, int DM, int PARTS>
 int launch_delta_scan_as(const T* v, int v_stride, int v_col, const float* qn, const float* kn, const float* kq, const float* decay,
                          const float* beta, float* state, const int* seq_starts, const int* seq_slots, float* out, int H, int G, int D, int DV,
-                         int R, bool alone, cudaStream_t s) {
-    constexpr int cols = SCAN_THREADS / PARTS;
-    const dim3 grid((DV + cols - 1) / cols, H, R);
-    const size_t smem = sizeof(float) * (2 * SCAN_TILE * (3 * DM + 2 + cols));
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<T, DM, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_kernel_on(alone, delta_scan_kernel<T, DM, PARTS>, grid, dim3(SCAN_THREADS), smem, s, v, v_stride, v_col, qn, kn, kq, decay, beta,
-                            state, seq_starts, seq_slots, out, H, G, D, DV);
+                         int R, bool alone, bool scalar, cudaStream_t s) {
+    if (scalar)
+        return launch_delta_scan_one<T, DM, PARTS, true>(v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, s);
+    return launch_delta_scan_one<T, DM, PARTS, false>(v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, s);
 }
 
 template <typename T, int NM, int PARTS>
@@ -494,8 +637,8 @@ int launch_ssm_scan_as(const T* xbc, int x_stride, int x_col, int b_col, int c_c
 template <typename T>
 int launch_delta_scan(const T* v, int v_stride, int v_col, const float* qn, const float* kn, const float* kq, const float* decay,
                       const float* beta, float* state, const int* seq_starts, const int* seq_slots, float* out, int H, int G, int D,
-                      int DV, int R, bool alone, cudaStream_t s) {
-    LLMIE_SCAN_DISPATCH(launch_delta_scan_as, D, v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, s)
+                      int DV, int R, bool alone, bool scalar, cudaStream_t s) {
+    LLMIE_SCAN_DISPATCH(launch_delta_scan_as, D, v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, scalar, s)
 }
 
 template <typename T>
@@ -504,6 +647,27 @@ int launch_ssm_scan(const T* xbc, int x_stride, int x_col, int b_col, int c_col,
                     int H, int G, int NS, int DV, int R, bool alone, cudaStream_t s) {
     LLMIE_SCAN_DISPATCH(launch_ssm_scan_as, NS, xbc, x_stride, x_col, b_col, c_col, dt_raw, dt_stride, A_log, dt_bias, Dskip, state, seq_starts,
                         seq_slots, out, H, G, NS, DV, R, alone, s)
+}
+
+template <typename T, int NM, int PARTS>
+int launch_selective_scan_as(const T* x, int x_stride, const T* dt_raw, int dt_stride, const T* bc, int bc_stride, int b_col, int c_col, const T* z,
+                             int z_stride, const float* A_log, const float* dt_bias, const float* Dskip, float* state, const int* seq_starts,
+                             const int* seq_slots, T* out, int C, int NS, int R, bool alone, cudaStream_t s) {
+    constexpr int cols = SCAN_THREADS / PARTS;
+    const dim3 grid((C + cols - 1) / cols, 1, R);
+    const size_t smem = sizeof(float) * (2 * SCAN_TILE * (2 * NM + 3 * cols));
+    if (smem > 48 * 1024) cudaFuncSetAttribute(selective_scan_kernel<T, NM, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_kernel_on(alone, selective_scan_kernel<T, NM, PARTS>, grid, dim3(SCAN_THREADS), smem, s, x, x_stride, dt_raw, dt_stride, bc, bc_stride,
+                            b_col, c_col, z, z_stride, A_log, dt_bias, Dskip, state, seq_starts, seq_slots, out, C, NS);
+}
+
+template <typename T>
+int launch_selective_scan(const T* x, int x_stride, const T* dt_raw, int dt_stride, const T* bc, int bc_stride, int b_col, int c_col, const T* z,
+                          int z_stride, const float* A_log, const float* dt_bias, const float* Dskip, float* state, const int* seq_starts,
+                          const int* seq_slots, T* out, int C, int NS, int R, bool alone, cudaStream_t s) {
+    const int H = C, DV = 1;   // (the channels are the columns that fill the device)
+    LLMIE_SCAN_DISPATCH(launch_selective_scan_as, NS, x, x_stride, dt_raw, dt_stride, bc, bc_stride, b_col, c_col, z, z_stride, A_log, dt_bias, Dskip,
+                        state, seq_starts, seq_slots, out, C, NS, R, alone, s)
 }
 
 }  // namespace
@@ -522,27 +686,27 @@ LLMIE_API int llmie_causal_conv(const void* z, int z_stride, int C, const float*
 
 LLMIE_API int llmie_delta_prepare(const void* qkv, int qkv_stride, int q_col, int k_col, const void* a, int a_stride, const void* b,
                                   int b_stride, const float* A_log, const float* dt_bias, float* qn, float* kn, float* kq, float* decay,
-                                  float* beta, int N, int H, int G, int D, float q_scale, float unit_eps, int dtype, cudaStream_t s) {
+                                  float* beta, int N, int H, int G, int D, float q_scale, float unit_eps, int per_head, int dtype, cudaStream_t s) {
     if (N <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0) return LLMIE_ERR_BAD_ARGUMENT;
     const dim3 grid(((size_t)N * H + 3) / 4);
     if (dtype == DT_F32)
         return launch_kernel(delta_prepare_kernel<float>, grid, dim3(128), 0, s, (const float*)qkv, qkv_stride, q_col, k_col, (const float*)a,
-                             a_stride, (const float*)b, b_stride, A_log, dt_bias, qn, kn, kq, decay, beta, N, H, G, D, q_scale, unit_eps);
+                             a_stride, (const float*)b, b_stride, A_log, dt_bias, qn, kn, kq, decay, beta, N, H, G, D, q_scale, unit_eps, per_head);
     return launch_kernel(delta_prepare_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)qkv, qkv_stride, q_col, k_col, (const bf16*)a, a_stride,
-                         (const bf16*)b, b_stride, A_log, dt_bias, qn, kn, kq, decay, beta, N, H, G, D, q_scale, unit_eps);
+                         (const bf16*)b, b_stride, A_log, dt_bias, qn, kn, kq, decay, beta, N, H, G, D, q_scale, unit_eps, per_head);
 }
 
-// state [slots][H][DV][D] float (column by column); out [N][H * DV] float
+// state [slots][H][DV][D] float (column by column); out [N][H * DV] float; decay [N][H][D], or [N][H] with per_head
 LLMIE_API int llmie_delta_scan(const void* v, int v_stride, int v_col, const float* qn, const float* kn, const float* kq,
                                const float* decay, const float* beta, float* state, const int* seq_starts, const int* seq_slots,
-                               float* out, int H, int G, int D, int DV, int R, int max_rows, int dtype, cudaStream_t s) {
+                               float* out, int H, int G, int D, int DV, int R, int max_rows, int per_head, int dtype, cudaStream_t s) {
     if (R <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || D > 256 || DV <= 0 || H > 65535 || R > 65535) return LLMIE_ERR_BAD_ARGUMENT;
     const bool alone = max_rows >= SCAN_ALONE_ROWS;   // a long walk: see launch_kernel_on
     if (dtype == DT_F32)
-        return launch_delta_scan<float>((const float*)v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, s);
-    return launch_delta_scan<bf16>((const bf16*)v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, s);
+        return launch_delta_scan<float>((const float*)v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, per_head != 0, s);
+    return launch_delta_scan<bf16>((const bf16*)v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, per_head != 0, s);
 }
 
 // state [slots][H][DV][NS] float (column by column); out [N][H * DV] float
@@ -557,4 +721,20 @@ LLMIE_API int llmie_ssm_scan(const void* xbc, int x_stride, int x_col, int b_col
                                       state, seq_starts, seq_slots, out, H, G, NS, DV, R, alone, s);
     return launch_ssm_scan<bf16>((const bf16*)xbc, x_stride, x_col, b_col, c_col, (const bf16*)dt_raw, dt_stride, A_log, dt_bias, Dskip, state,
                                  seq_starts, seq_slots, out, H, G, NS, DV, R, alone, s);
+}
+
+// x, dt_raw, z: [N] rows of C channels (the caller offsets the pointers to their first column); bc: rows that hold B from column
+// b_col and C from column c_col (NS entries each); A_log [C][NS], dt_bias [C], Dskip [C]; state [slots][C][NS] float; out [N][C].
+LLMIE_API int llmie_selective_scan(const void* x, int x_stride, const void* dt_raw, int dt_stride, const void* bc, int bc_stride, int b_col,
+                                   int c_col, const void* z, int z_stride, const float* A_log, const float* dt_bias, const float* Dskip,
+                                   float* state, const int* seq_starts, const int* seq_slots, void* out, int C, int NS, int R, int max_rows,
+                                   int dtype, cudaStream_t s) {
+    if (R <= 0) return 0;
+    if (C <= 0 || NS <= 0 || NS > 256 || R > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    const bool alone = max_rows >= SCAN_ALONE_ROWS;
+    if (dtype == DT_F32)
+        return launch_selective_scan<float>((const float*)x, x_stride, (const float*)dt_raw, dt_stride, (const float*)bc, bc_stride, b_col, c_col,
+                                            (const float*)z, z_stride, A_log, dt_bias, Dskip, state, seq_starts, seq_slots, (float*)out, C, NS, R, alone, s);
+    return launch_selective_scan<bf16>((const bf16*)x, x_stride, (const bf16*)dt_raw, dt_stride, (const bf16*)bc, bc_stride, b_col, c_col,
+                                       (const bf16*)z, z_stride, A_log, dt_bias, Dskip, state, seq_starts, seq_slots, (bf16*)out, C, NS, R, alone, s);
 }

@@ -68,3 +68,25 @@ class SandwichBlock(Part):
             y = K.zeros_like_rows(residual)
             self.ff.forward(ctx, h, y)
             self.norm2b.add_normed(ctx, residual, y)
+
+
+class ParallelBlock(Part):
+    """``h = norm(x); x += mixer(h) + ff(h)``: one norm, and both sublayers read its output. Each sublayer adds its result into
+    the 32-bit stream itself, so the sum of the two is never a tensor of its own; a layer may be a mixer alone."""
+
+    graph_safe = True
+
+    def __init__(self, norm: Norm, mixer: Mixer, ff: Optional[FeedForward] = None):
+        self.norm, self.mixer, self.ff = norm, mixer, ff
+
+    def children(self) -> Sequence[Part]:
+        return tuple(p for p in (self.norm, self.mixer, self.ff) if p is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx, residual: torch.Tensor, cache) -> None:
+        h = self.norm.norm(ctx, residual)   # (the stream is read here, before either sublayer adds into it)
+        self.mixer.forward(ctx, h, cache, residual)
+        if self.ff is not None:
+            self.ff.forward(ctx, h, residual)

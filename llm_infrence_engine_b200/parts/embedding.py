@@ -29,12 +29,14 @@ class TokenEmbedding(Part):
 
 class OutputHead(Part):
     """``logits = h W^T`` without bias, in 32-bit. ``tied_to`` makes ``W`` the embedding's own table
-    (src/miniserve/model.py:204-206); a tensor of the head's name in the checkpoint is then not needed."""
+    (src/miniserve/model.py:204-206); a tensor of the head's name in the checkpoint is then not needed. ``softcap`` bounds the
+    logits: ``softcap * tanh(logits / softcap)``."""
 
     graph_safe = True
 
-    def __init__(self, vocab: int, hidden: int, name: str, tied_to: Optional[TokenEmbedding] = None):
+    def __init__(self, vocab: int, hidden: int, name: str, tied_to: Optional[TokenEmbedding] = None, softcap: Optional[float] = None):
         self.vocab, self.hidden, self.name, self.tied_to = vocab, hidden, name, tied_to
+        self.softcap = float(softcap) if softcap else None
         self.weight: Optional[torch.Tensor] = None
 
     def params(self) -> Dict[str, ParamSpec]:
@@ -54,4 +56,5 @@ class OutputHead(Part):
         return self.tied_to.table if self.tied_to is not None else self.weight
 
     def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
-        return ctx.K.linear(h, self.matrix(), out_dtype=torch.float32)
+        logits = ctx.K.linear(h, self.matrix(), out_dtype=torch.float32)
+        return ctx.K.softcap(logits, self.softcap) if self.softcap else logits

@@ -5,7 +5,7 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import MATRIX, FeedForward, ParamSpec, Source
+from .base import INIT_PROJ, INIT_SMALL, MATRIX, VECTOR, FeedForward, ParamSpec, Source
 
 ACTIVATIONS = ("silu",)
 
@@ -87,3 +87,78 @@ class ClampedGLU(FeedForward):
     def forward(self, ctx, h, residual):
         K = ctx.K
         K.linear(K.gate_up_act(h, self.w_gate_up, ctx.dtype, glu=(self.limit, self.alpha, self.shift)), self.w_down, add_to=residual)
+
+
+class GatedUnit(FeedForward):
+    """``down(act(gate(x)) * up(x))`` without biases, under checkpoint names of the caller's choice; ``act`` is ``silu`` or the
+    tanh form of GELU, ``0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``. ``gate`` and ``up`` are one matrix (gate rows first);
+    the activation is the epilogue of that product (prompt portions) or one kernel over its float32 sums (decode steps)."""
+
+    graph_safe = True
+    ACTIVATIONS = ("silu", "gelu_tanh")
+
+    def __init__(self, hidden: int, intermediate: int, gate_name: str, up_name: str, down_name: str, activation: str = "silu"):
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"activation '{activation}' is not one of {self.ACTIVATIONS}")
+        self.hidden, self.intermediate, self.activation = hidden, intermediate, activation
+        self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        h, i = self.hidden, self.intermediate
+        return {"w_gate_up": ParamSpec((Source(self.gate_name, (i, h), INIT_PROJ), Source(self.up_name, (i, h), INIT_PROJ)), MATRIX),
+                "w_down": ParamSpec((Source(self.down_name, (h, i), INIT_PROJ),), MATRIX)}
+
+    def forward(self, ctx, h, residual):
+        K = ctx.K
+        K.linear(K.gate_up_act(h, self.w_gate_up, ctx.dtype, activation=self.activation), self.w_down, add_to=residual)
+
+
+class RoutedExperts(FeedForward):
+    """``num_experts`` gated units (``down(silu(gate x) * (up x))``, no biases) of which every token uses ``top``, chosen by a router:
+
+        s = softmax(W_router x) over all router outputs, in 32-bit;   choice = s + correction;
+        the ``top`` outputs with the largest choice are taken; their weights are ``s / (sum of the taken s + 1e-20)``.
+
+    The router has ``num_identity`` outputs more than there are experts with matrices: a token that takes one of them gets its own
+    input back from it (times the weight). ``shared`` (a feed-forward of its own, or None) runs for every token and is added.
+    Checkpoint names: ``{prefix}.router``, ``{prefix}.correction``, ``{prefix}.e<i>.gate / up / down``. The experts' matrices are
+    kept stacked (``[E, 2 ff, hidden]`` and ``[E, hidden, ff]``); tokens are sorted by expert on the device and every expert's
+    rows pass its matrices in one grouped product, so the part only launches kernels."""
+
+    graph_safe = True
+
+    def __init__(self, hidden: int, intermediate: int, num_experts: int, num_identity: int, top: int, prefix: str,
+                 shared: Optional[FeedForward] = None):
+        if not 1 <= top <= num_experts + num_identity:
+            raise ValueError(f"{top} of {num_experts + num_identity} router outputs cannot be chosen")
+        self.hidden, self.intermediate, self.num_experts, self.num_identity, self.top = hidden, intermediate, num_experts, num_identity, top
+        self.prefix, self.shared = prefix, shared
+        self.w_router = self.correction = self.w_gate_up = self.w_down = None
+
+    def children(self):
+        return (self.shared,) if self.shared is not None else ()
+
+    def params(self) -> Dict[str, ParamSpec]:
+        p, h, i, E = self.prefix, self.hidden, self.intermediate, self.num_experts
+        total = E + self.num_identity
+        gate_up = tuple(Source(f"{p}.e{e}.{n}", (i, h), INIT_PROJ) for e in range(E) for n in ("gate", "up"))
+        return {"w_router": ParamSpec((Source(f"{p}.router", (total, h), INIT_PROJ),), MATRIX),
+                "correction": ParamSpec((Source(f"{p}.correction", (total,), INIT_SMALL),), VECTOR),
+                "w_gate_up": ParamSpec(gate_up, MATRIX),
+                "w_down": ParamSpec(tuple(Source(f"{p}.e{e}.down", (h, i), INIT_PROJ) for e in range(E)), MATRIX)}
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        E, h, i = self.num_experts, self.hidden, self.intermediate
+        self.w_gate_up = self.w_gate_up.view(E, 2 * i, h)
+        self.w_down = self.w_down.view(E, h, i)
+
+    def forward(self, ctx, h, residual):
+        K = ctx.K
+        logits = K.linear(h, self.w_router, out_dtype=torch.float32)
+        ids, weights = K.moe_route(logits, self.correction, self.top)
+        K.moe_experts(h, ids, weights, self.w_gate_up, self.w_down, add_to=residual)
+        if self.shared is not None:
+            self.shared.forward(ctx, h, residual)

@@ -48,8 +48,8 @@ class RMSNorm(Norm):
 
 
 class LayerNorm(Norm):
-    """``y = (x - mean) / sqrt(var + eps) * weight`` without a bias, the variance being the mean squared deviation; mean,
-    variance and scaling in 32-bit, one rounding of the result.
+    """``y = (x - mean) / sqrt(var + eps) * weight`` (``+ bias`` where ``bias_name`` names one), the variance being the mean
+    squared deviation; mean, variance and scaling in 32-bit, one rounding of the result.
 
     The same norm also closes a sublayer: ``add_normed(ctx, residual, y)`` is ``residual += norm(y)``. That addition is put
     off until the next norm of the stream, whose kernel adds and normalises in one pass.
@@ -57,18 +57,28 @@ class LayerNorm(Norm):
 
     graph_safe = True
 
-    def __init__(self, dim: int, eps: float, weight_name: str):
-        self.dim, self.eps, self.weight_name = dim, float(eps), weight_name
+    def __init__(self, dim: int, eps: float, weight_name: str, bias_name: Optional[str] = None):
+        self.dim, self.eps, self.weight_name, self.bias_name = dim, float(eps), weight_name, bias_name
         self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
 
     def params(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((Source(self.weight_name, (self.dim,), INIT_NORM),), VECTOR)}
+        out = {"weight": ParamSpec((Source(self.weight_name, (self.dim,), INIT_NORM),), VECTOR)}
+        if self.bias_name is not None:
+            out["bias"] = ParamSpec((Source(self.bias_name, (self.dim,), INIT_SMALL),), VECTOR)
+        return out
 
     def norm(self, ctx, residual):
-        return ctx.K.layernorm(residual, self.weight, self.eps, ctx.dtype)
+        if self.bias is None:
+            return ctx.K.layernorm(residual, self.weight, self.eps, ctx.dtype)
+        return ctx.K.layernorm(residual, self.weight, self.eps, ctx.dtype, bias=self.bias)
 
     def norm_rows(self, ctx, residual, rows):
-        return ctx.K.layernorm(residual, self.weight, self.eps, ctx.dtype, rows)
+        if self.bias is None:
+            return ctx.K.layernorm(residual, self.weight, self.eps, ctx.dtype, rows)
+        return ctx.K.layernorm(residual, self.weight, self.eps, ctx.dtype, rows, bias=self.bias)
 
     def add_normed(self, ctx, residual, y) -> None:
+        if self.bias is not None:
+            raise ValueError("a layer norm with a bias does not close a sublayer here")
         ctx.K.post_norm_add(residual, y, self.weight, self.eps)

@@ -171,19 +171,158 @@ class StateSpaceMixer(Mixer):
         K.linear(y, self.w_o, add_to=residual)
 
 
-class ParallelMixer(Mixer):
-    """Two mixers side by side on the same input: the result is half the sum of their outputs, each first divided by its root
-    mean square over the model width and multiplied by a weight of its own. Each keeps its own cache or state."""
+class HeadDecayDeltaMixer(Mixer):
+    """The gated delta rule with ONE decay per head. With q, k of ``num_kv_heads x head_dim`` and v of ``num_heads x v_head_dim``
+    (head ``h`` uses q/k head ``h // (num_heads // num_kv_heads)``), each through a short causal convolution and SiLU, q and k then
+    made unit vectors per head (``x / sqrt(sum x^2 + 1e-6)``, q also times ``head_dim^-1/2``):
+
+        beta = sigmoid(W_b x)                                           one per head
+        g    = exp(-exp(A_log[h]) * softplus(W_a x + dt_bias[h]))       one per head
+        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+
+    per head, ``S [head_dim, v_head_dim]`` starting at zero. Each head's ``o`` is divided by its root mean square, multiplied by a
+    weight shared by the heads and by ``silu(W_g x)``; then the output projection. All six projections of the input are one
+    matrix. Decays, gates, unit norms and the state are 32-bit; a request's state is ``S`` and the convolution's last
+    ``conv_taps - 1`` inputs. Checkpoint names: ``{prefix}.q / k / v`` (+ ``.conv``), ``.b``, ``.a``, ``.g``, ``.o``, ``.A_log``,
+    ``.dt_bias``, ``.norm``."""
 
     graph_safe = True
 
-    def __init__(self, hidden: int, left: Mixer, right: Mixer, eps: float, left_weight: str, right_weight: str):
+    def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, conv_taps: int, eps: float, prefix: str):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} query/key heads")
+        if not 1 <= conv_taps <= 8:
+            raise ValueError(f"a short convolution has 1 to 8 taps, got {conv_taps}")
+        if head_dim > 256:
+            raise ValueError(f"the delta rule's kernel keeps a column of the state in registers: head_dim {head_dim} is more than 256")
+        self.hidden, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim = hidden, num_heads, num_kv_heads, head_dim, v_head_dim
+        self.conv_taps, self.eps, self.prefix = int(conv_taps), float(eps), prefix
+        self.qk = num_kv_heads * head_dim
+        self.channels = 2 * self.qk + num_heads * v_head_dim      # what the convolution sees: q | k | v
+        self.b_col = self.a_col = self.g_col = 0      # columns of the joined projection's sections: set when the weights are bound
+        self.w_in = self.w_o = self.conv_w = self.A_log = self.dt_bias = self.norm_w = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        p, h, H, DV = self.prefix, self.hidden, self.num_heads, self.v_head_dim
+        rows = (("q", self.qk), ("k", self.qk), ("v", H * DV))
+        return {
+            "w_in": ParamSpec(tuple(Source(f"{p}.{n}", (c, h), INIT_PROJ) for n, c in rows)
+                              + (Source(f"{p}.b", (H, h), INIT_PROJ), Source(f"{p}.a", (H, h), INIT_PROJ), Source(f"{p}.g", (H * DV, h), INIT_PROJ)), MATRIX),
+            "w_o": ParamSpec((Source(f"{p}.o", (h, H * DV), INIT_PROJ),), MATRIX),
+            "conv_w": ParamSpec(tuple(Source(f"{p}.{n}.conv", (c, self.conv_taps), INIT_TAPS) for n, c in rows), VECTOR),
+            "A_log": ParamSpec((Source(f"{p}.A_log", (H,), INIT_LOG_RATE),), VECTOR),
+            "dt_bias": ParamSpec((Source(f"{p}.dt_bias", (H,), INIT_STEP_BIAS),), VECTOR),
+            "norm_w": ParamSpec((Source(f"{p}.norm", (DV,), INIT_NORM),), VECTOR),
+        }
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        H = self.num_heads
+        # every section of the joined projection starts on a multiple of 8 rows: its columns of the product then start on a
+        # 16-byte boundary
+        pieces, starts, at = [], [], 0
+        for part in torch.split(self.w_in, (self.channels, H, H, H * self.v_head_dim)):
+            starts.append(at)
+            pieces.append(_padded(part))
+            at += pieces[-1].shape[0]
+        _, self.b_col, self.a_col, self.g_col = starts
+        self.w_in = torch.cat(pieces).contiguous()
+
+    def cache_spec(self):
+        return (FixedStateSpec((self.num_heads, self.v_head_dim, self.head_dim)), FixedStateSpec((self.conv_taps - 1, self.channels)))   # S column by column
+
+    def forward(self, ctx, h, cache, residual):
+        K = ctx.K
+        state, conv_state = cache
+        H, G, D, DV = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        z = K.linear(h, self.w_in, out_dtype=ctx.dtype)
+        qkv = K.causal_conv(z, 0, self.channels, self.conv_w, None, conv_state.state, ctx, activation="silu")
+        o = K.delta_rule(qkv, H, G, D, DV, z[:, self.a_col:self.a_col + H], z, self.b_col, self.A_log, self.dt_bias, state.state, ctx, decay_per_head=True)
+        y = K.group_rmsnorm_gate(o, z, self.g_col, self.norm_w, DV, self.eps, gate_first=False, out_dtype=ctx.dtype, gate_act="silu")
+        K.linear(y, self.w_o, add_to=residual)
+
+
+class SelectiveScanMixer(Mixer):
+    """A selective scan with a state per channel and state index (the recurrence of Mamba). ``W_in x`` is ``[x: inner | z: inner]``;
+    x passes a short causal convolution with a bias and SiLU; ``W_x x`` is ``[dt: dt_rank | B: state | C: state]``;
+    ``dt <- softplus(W_dt dt + dt_bias)``, one per channel; ``A = -exp(A_log)`` ``[inner, state]``; per channel c and state index n:
+
+        S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n;   y_c = sum_n S[c, n] C_n + D_c x_c
+
+    then ``y * silu(z)`` and the output projection. Step sizes, decays and the state are 32-bit; a request's state is ``S``
+    (starting at zero) and the convolution's last ``conv_taps - 1`` inputs. Checkpoint names: ``{prefix}.in``, ``.conv`` (+ ``.b``),
+    ``.x``, ``.dt`` (+ ``.b``), ``.A_log``, ``.D``, ``.o``."""
+
+    graph_safe = True
+
+    def __init__(self, hidden: int, inner: int, state_size: int, dt_rank: int, conv_taps: int, prefix: str):
+        if not 1 <= conv_taps <= 8:
+            raise ValueError(f"a short convolution has 1 to 8 taps, got {conv_taps}")
+        if state_size > 256:
+            raise ValueError(f"the recurrence's kernel keeps a channel's state in registers: state size {state_size} is more than 256")
+        self.hidden, self.inner, self.state_size, self.dt_rank, self.conv_taps, self.prefix = hidden, inner, state_size, dt_rank, int(conv_taps), prefix
+        self.w_in = self.w_x = self.w_dt = self.w_o = self.conv_w = self.conv_b = self.dt_bias = self.A_log = self.skip = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        p, h, C, NS, R = self.prefix, self.hidden, self.inner, self.state_size, self.dt_rank
+        return {
+            "w_in": ParamSpec((Source(f"{p}.in", (2 * C, h), INIT_PROJ),), MATRIX),
+            "w_x": ParamSpec((Source(f"{p}.x", (R + 2 * NS, C), INIT_PROJ),), MATRIX),
+            "w_dt": ParamSpec((Source(f"{p}.dt", (C, R), INIT_PROJ),), MATRIX),
+            "w_o": ParamSpec((Source(f"{p}.o", (h, C), INIT_PROJ),), MATRIX),
+            "conv_w": ParamSpec((Source(f"{p}.conv", (C, self.conv_taps), INIT_TAPS),), VECTOR),
+            "conv_b": ParamSpec((Source(f"{p}.conv.b", (C,), INIT_SMALL),), VECTOR),
+            "dt_bias": ParamSpec((Source(f"{p}.dt.b", (C,), INIT_STEP_BIAS),), VECTOR),
+            "A_log": ParamSpec((Source(f"{p}.A_log", (C, NS), INIT_LOG_RATE),), VECTOR),
+            "skip": ParamSpec((Source(f"{p}.D", (C,), INIT_NORM),), VECTOR),
+        }
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        # ``W_x``'s rows are padded to a multiple of 8 (16-byte rows of the product), and ``W_dt`` gets zero columns for B, C and
+        # the padding, so that the step sizes are a product over the whole row of ``W_x x`` as it lies
+        self.w_x = _padded(self.w_x)
+        wide = self.w_dt.new_zeros((self.inner, self.w_x.shape[0]))
+        wide[:, :self.dt_rank] = self.w_dt
+        self.w_dt = wide.contiguous()
+
+    def cache_spec(self):
+        return (FixedStateSpec((self.inner, self.state_size)), FixedStateSpec((self.conv_taps - 1, self.inner)))
+
+    def forward(self, ctx, h, cache, residual):
+        K = ctx.K
+        state, conv_state = cache
+        C, NS, R = self.inner, self.state_size, self.dt_rank
+        xz = K.linear(h, self.w_in, out_dtype=ctx.dtype)
+        x = K.causal_conv(xz, 0, C, self.conv_w, self.conv_b, conv_state.state, ctx, activation="silu")
+        dbc = K.linear(x, self.w_x, out_dtype=ctx.dtype)
+        dt = K.linear(dbc, self.w_dt, out_dtype=ctx.dtype)
+        y = K.selective_scan(x, dt, dbc, R, R + NS, xz, C, self.A_log, self.dt_bias, self.skip, state.state, ctx)
+        K.linear(y, self.w_o, add_to=residual)
+
+
+class ParallelMixer(Mixer):
+    """Two mixers side by side on the same input, each with its own cache or state. Two ways of joining their outputs:
+
+    * normed mean (``left_weight``, ``right_weight`` name two vectors of the checkpoint): half the sum of the outputs, each first
+      divided by its root mean square over the model width and multiplied by its vector;
+    * ``scales = (a, b)``: ``a * left + b * right``, nothing else."""
+
+    graph_safe = True
+
+    def __init__(self, hidden: int, left: Mixer, right: Mixer, eps: float, left_weight: Optional[str] = None, right_weight: Optional[str] = None,
+                 scales: Optional[tuple] = None):
+        if (scales is None) == (left_weight is None) or (left_weight is None) != (right_weight is None):
+            raise ValueError("two mixers side by side are joined by two named weight vectors or by two scales, not both")
         self.hidden, self.left, self.right, self.eps = hidden, left, right, float(eps)
         self.left_weight, self.right_weight = left_weight, right_weight
+        self.scales = None if scales is None else (float(scales[0]), float(scales[1]))
         self.w_left: Optional[torch.Tensor] = None
         self.w_right: Optional[torch.Tensor] = None
 
     def params(self) -> Dict[str, ParamSpec]:
+        if self.scales is not None:
+            return {}
         return {"w_left": ParamSpec((Source(self.left_weight, (self.hidden,), INIT_NORM),), VECTOR),
                 "w_right": ParamSpec((Source(self.right_weight, (self.hidden,), INIT_NORM),), VECTOR)}
 
@@ -201,4 +340,7 @@ class ParallelMixer(Mixer):
         b = K.zeros_like_rows(residual, 2)
         self.right.forward(ctx, h, cache[1], b)
         b = K.take_result(b)
-        K.dual_rmsnorm_mix(a, b, self.w_left, self.w_right, self.eps, 0.5, add_to=residual)
+        if self.scales is not None:
+            K.weighted_pair(a, b, self.scales[0], self.scales[1], add_to=residual)
+        else:
+            K.dual_rmsnorm_mix(a, b, self.w_left, self.w_right, self.eps, 0.5, add_to=residual)

@@ -116,7 +116,12 @@ class TorchKernels:
                 out[t, h] = pr @ v[:, h // rep]
         return out.reshape(N, num_heads * d).to(qkv.dtype)
 
-    def gate_up_act(self, x, w_gate_up, out_dtype=None, glu=None):
+    def gate_up_act(self, x, w_gate_up, out_dtype=None, glu=None, activation="silu"):
+        if activation == "gelu_tanh":
+            gu = self.linear(x, w_gate_up, out_dtype=torch.float32)
+            i = gu.shape[1] // 2
+            g, u = gu[:, :i], gu[:, i:]
+            return (0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3))) * u).to(out_dtype or x.dtype)
         if glu is not None:
             return self.glu_clamped(self.linear(x, w_gate_up, out_dtype=torch.float32), *glu, out_dtype or x.dtype)
         return self.silu_mul(self.linear(x, w_gate_up, out_dtype=torch.float32)).to(out_dtype or x.dtype)
@@ -212,14 +217,15 @@ class TorchKernels:
         d = x - mu
         return d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * w.float()
 
-    def layernorm(self, residual, weight, eps, out_dtype, rows=None):
+    def layernorm(self, residual, weight, eps, out_dtype, rows=None, bias=None):
         x = residual if rows is None else residual[rows.long()]
-        return self._ln(x, weight, eps).to(out_dtype)
+        y = self._ln(x, weight, eps)
+        return (y if bias is None else y + bias.float()).to(out_dtype)
 
     def post_norm_add(self, residual, y, weight, eps):
         residual += self._ln(y.float(), weight, eps)
 
-    def group_rmsnorm_gate(self, x, gate, gate_col, weight, group_size, eps, gate_first, out_dtype):
+    def group_rmsnorm_gate(self, x, gate, gate_col, weight, group_size, eps, gate_first, out_dtype, gate_act="sigmoid"):
         N, C = x.shape
         z = gate[:, gate_col:gate_col + C].float()
         v = x * (z * torch.sigmoid(z)) if gate_first else x
@@ -227,8 +233,14 @@ class TorchKernels:
         v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).reshape(N, C)
         v = v * (weight.float() if weight.shape[0] == C else weight.float().repeat(C // group_size))
         if not gate_first:
-            v = v * torch.sigmoid(z)
+            v = v * (z * torch.sigmoid(z) if gate_act == "silu" else torch.sigmoid(z))
         return v.to(out_dtype)
+
+    def weighted_pair(self, a, b, coef_a, coef_b, add_to):
+        add_to += coef_a * a.float() + coef_b * b.float()
+
+    def softcap(self, x, cap):
+        return cap * torch.tanh(x / cap)
 
     def dual_rmsnorm_mix(self, a, b, weight_a, weight_b, eps, coef, add_to):
         a, b = a.float(), b.float()
@@ -293,7 +305,8 @@ class TorchKernels:
             state[slot] = u[u.shape[0] - (taps - 1):]
         return out.to(z.dtype)
 
-    def delta_rule(self, qkv, num_heads, num_kv_heads, head_dim, v_head_dim, a, b, b_col, A_log, dt_bias, state, batch, unit_eps=1e-6):
+    def delta_rule(self, qkv, num_heads, num_kv_heads, head_dim, v_head_dim, a, b, b_col, A_log, dt_bias, state, batch, unit_eps=1e-6,
+                   decay_per_head=False):
         N = qkv.shape[0]
         H, G, D, DV = num_heads, num_kv_heads, head_dim, v_head_dim
         x = qkv.float()
@@ -301,7 +314,10 @@ class TorchKernels:
         q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + unit_eps) * D ** -0.5
         k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)
         beta = torch.sigmoid(b[:, b_col:b_col + H].float())
-        decay = torch.exp(-torch.exp(A_log.float())[None, :, None] * torch.nn.functional.softplus(a.float() + dt_bias.float()).view(N, H, D))
+        if decay_per_head:
+            decay = torch.exp(-torch.exp(A_log.float())[None, :] * torch.nn.functional.softplus(a.float() + dt_bias.float()))[:, :, None].expand(N, H, D)
+        else:
+            decay = torch.exp(-torch.exp(A_log.float())[None, :, None] * torch.nn.functional.softplus(a.float() + dt_bias.float()).view(N, H, D))
         out = torch.zeros(N, H, DV)
         for slot, s0, s1 in self._requests(batch):
             for h in range(H):
@@ -332,6 +348,45 @@ class TorchKernels:
                     out[n, h] = S.T @ C[n, g] + skip[h] * x[n, h]
                 state[slot, h] = S.T
         return out.reshape(N, H * DV)
+
+    def selective_scan(self, x, dt, bc, b_col, c_col, z, z_col, A_log, dt_bias, skip, state, batch):
+        N, C = x.shape
+        NS = A_log.shape[1]
+        xf = x.float()
+        step = torch.nn.functional.softplus(dt.float() + dt_bias.float())
+        B, Cc = bc[:, b_col:b_col + NS].float(), bc[:, c_col:c_col + NS].float()
+        A = -torch.exp(A_log.float())
+        gate = z[:, z_col:z_col + C].float()
+        out = torch.zeros(N, C)
+        for slot, s0, s1 in self._requests(batch):
+            S = state[slot].clone()                  # [channels, state_size]
+            for n in range(s0, s1):
+                S = torch.exp(step[n][:, None] * A) * S + (step[n] * xf[n])[:, None] * B[n][None, :]
+                out[n] = (S @ Cc[n] + skip.float() * xf[n]) * (gate[n] * torch.sigmoid(gate[n]))
+            state[slot] = S
+        return out.to(x.dtype)
+
+    # ------------------------------------------------------------------ routed experts
+    def moe_route(self, logits, correction, top):
+        s = torch.softmax(logits.float(), dim=-1)
+        choice = s if correction is None else s + correction.float()
+        ids = torch.topk(choice, top, dim=-1).indices
+        w = torch.gather(s, 1, ids)
+        return ids.to(torch.int32), w / (w.sum(-1, keepdim=True) + 1e-20)
+
+    def moe_experts(self, h, ids, weights, w_gate_up, w_down, add_to):
+        E, F = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+        x = h.float()
+        for t in range(h.shape[0]):
+            for k in range(ids.shape[1]):
+                e = int(ids[t, k])
+                if e < E:
+                    gu = w_gate_up[e].float() @ x[t]
+                    act = (gu[:F] * torch.sigmoid(gu[:F]) * gu[F:]).to(h.dtype).float()
+                    y = w_down[e].float() @ act
+                else:
+                    y = x[t]
+                add_to[t] += weights[t, k] * y
 
     # ------------------------------------------------------------------ latent attention
     @staticmethod
