@@ -20,8 +20,9 @@ batch of 8 requests and a context of 8192 tokens. A "step" is one decode step of
 ``roofline``  bytes a decode step must read (every weight once + the live requests' cache) / its time.
 ``points``    decode tokens per second at batch 1 and 64, same method as ``value``.
 
-``--workload serving | luvutar | zepalorn`` measure other things (a stream of requests through the engine; the two other architectures
-beside Qwen2 of equal size, with ``--kernels`` also kernel by kernel) and print lines of their own; the default line is unchanged by them.
+``--workload serving | luvutar | zepalorn | mufotar`` measure other things (a stream of requests through the engine; the other architectures
+beside Qwen2 of equal size, Mufotar beside Zepalorn, with ``--kernels`` also kernel by kernel) and print lines of their own; the default line is
+unchanged by them.
 
 Peaks come from MEASURED_PEAKS.json beside this file when it exists, else 6.65 TB/s and 1.59 PFLOP/s.
 More than one GPU is outside this engine: ``--gpus N`` with N > 1 prints one line and exits with 2.
@@ -944,6 +945,184 @@ def zepalorn_workload(a) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# ``--workload mufotar``: the Mufotar decoder at layer sizes of real models, beside the Zepalorn decoder (the closest of the
+# engine's other models: delta rule, attention beside a recurrence) of equal width, layers and activated feed-forward size.
+
+MUFOTAR_SIZES = {
+    # name: (width, delta heads, delta q/k heads, delta key size, delta value size, attention heads, kv heads, head_dim, scan channels,
+    #        scan state, step-size rank, experts, identity experts, chosen, expert ff, shared ff, dense ff, layers, vocab)
+    "1b-like": (1024, 8, 4, 128, 128, 8, 2, 128, 2048, 16, 64, 16, 2, 4, 512, 768, 2816, 8, 32768),
+    "3b-like": (2048, 16, 8, 128, 128, 16, 4, 128, 4096, 16, 128, 32, 2, 4, 768, 2432, 5504, 8, 32768),
+}
+MUFOTAR_NAMES = ("width", "delta_heads", "delta_qk_heads", "delta_dim", "delta_vdim", "heads", "kv_heads", "head_dim", "scan_channels", "scan_state",
+                 "dt_rank", "experts", "identity_experts", "top", "expert_ff", "shared_ff", "dense_ff", "layers", "vocab")
+
+
+def mufotar_config(size: str) -> dict:
+    """Layers in the order delta rule (dense feed-forward), delta rule, attention beside a selective scan, delta rule (routed
+    experts), twice; the second attention layer runs on the first one's weights."""
+    W, dh, dg, dd, dv, H, G, d, ci, ns, rk, E, ident, top, eff, sff, ff, layers, vocab = MUFOTAR_SIZES[size]
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "identity": ident, "top": top}, "shared": {"ff": sff}}
+    delta = {"heads": dh, "kv_heads": dg, "dim": dd, "vdim": dv, "conv": 4}
+    pair = {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": {"base": 250000.0, "dims": d}},
+            "right": {"inner": ci, "state": ns, "dt_rank": rk, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}
+    kinds = []
+    for i in range(layers):
+        if i % 4 == 2:
+            layer = {"type": "parallel", "mixer": pair, "mlp": moe}
+            if i > 2:
+                layer["weights_of"] = 2
+        else:
+            layer = {"type": "delta", "mixer": delta, "mlp": {"kind": "dense", "ff": ff} if i % 4 == 0 else moe}
+        kinds.append(layer)
+    return {"architecture": "Mufotar", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": kinds}
+
+
+def zepalorn_beside_mufotar(size: str) -> dict:
+    """Zepalorn with the same width, layer kinds in the same places (its delta rule has a decay per channel, its recurrence beside
+    the attention a state per head), and dense feed-forwards of the size that a Mufotar token activates (chosen experts + shared)."""
+    W, dh, dg, dd, dv, H, G, d, ci, ns, rk, E, ident, top, eff, sff, ff, layers, vocab = MUFOTAR_SIZES[size]
+    kinds = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff if i % 4 == 0 else top * eff + sff, "limit": 7.0}
+        if i % 4 == 2:
+            left = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "conv": 4, "rot": {"base": 250000.0, "dims": d}}
+            right = {"heads": ci // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}
+            kinds.append({"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp})
+        else:
+            kinds.append({"type": "channel_delta", "mixer": {"heads": dh, "kv_heads": dh, "dim": dd, "vdim": dv, "conv": 4}, "mlp": mlp})
+    return {"architecture": "Zepalorn", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": kinds}
+
+
+def mufotar_kernel_points(torch, pk) -> dict:
+    """Mufotar's kernels one by one at the 3b-like layer sizes, each beside the kernel of the engine's other models that does the
+    like job at the same size: microseconds, and the fraction of its roofline (bytes that must move / copy peak, or flops / bf16
+    peak). decode: 8 and 64 requests bring one token each; prefill: one request brings 2,048."""
+    from types import SimpleNamespace
+
+    from llm_infrence_engine_b200.csrc import get_kernels
+
+    K = get_kernels()
+    W, dh, dg, dd, dv, H, G, d, ci, ns, rk, E, ident, top, eff, sff, ff, _, _ = MUFOTAR_SIZES["3b-like"]
+    bf, dev = torch.bfloat16, "cuda"
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out = {}
+
+    def entry(us, bytes_=None, flops=None):
+        e = {"us": round(us, 2)}
+        if bytes_ is not None:
+            e["frac_of_copy_peak"] = round(bytes_ / (us * 1e-6) / hbm, 4)
+        if flops is not None:
+            e["frac_of_bf16_peak"] = round(flops / (us * 1e-6) / tf, 4)
+        return e
+
+    def batch_of(lens):
+        starts = [0]
+        for n in lens:
+            starts.append(starts[-1] + n)
+        return SimpleNamespace(seq_lens=list(lens), seq_starts_dev=torch.tensor(starts, dtype=torch.int32, device=dev), num_seqs=len(lens),
+                               seq_slots=torch.tensor(list(range(len(lens))), dtype=torch.int32, device=dev), max_seq_len=max(lens), _tables={})
+
+    for what, batch, T in (("decode", 8, 1), ("decode_b64", 64, 1), ("prefill", 1, 2048)):
+        N = batch * T
+        b = batch_of([T] * batch)
+        # the delta rule: a decay per head (Mufotar, q/k heads shared by two value heads) beside a decay per channel (Zepalorn)
+        qkv = torch.randn(N, 2 * dg * dd + dh * dv, device=dev).to(bf) * 0.5
+        z = torch.randn(N, 2 * dh, device=dev).to(bf)
+        A_log, bias = torch.zeros(dh, device=dev), torch.full((dh,), -3.0, device=dev)
+        state = torch.zeros(batch + 1, dh, dv, dd, device=dev)
+        moved = batch * 2 * 4 * dh * dd * dv + N * (2 * (2 * dg * dd + dh * dv) + 4 * dh * dv)
+        out[f"delta_rule_{what}_mufotar"] = entry(_time_graph(lambda: K.delta_rule(qkv, dh, dg, dd, dv, z[:, :dh], z, dh, A_log, bias, state, b, decay_per_head=True), torch),
+                                                  moved, 8.0 * N * dh * dd * dv)
+        qkv2 = torch.randn(N, 2 * dh * dd + dh * dv, device=dev).to(bf) * 0.5
+        a2, b2 = torch.randn(N, dh * dd, device=dev).to(bf), torch.randn(N, dh, device=dev).to(bf)
+        bias2 = torch.full((dh * dd,), -3.0, device=dev)
+        moved = batch * 2 * 4 * dh * dd * dv + N * (2 * (3 * dh * dd + dh * dv) + 4 * dh * dv)
+        out[f"delta_rule_{what}_zepalorn"] = entry(_time_graph(lambda: K.delta_rule(qkv2, dh, dh, dd, dv, a2, b2, 0, A_log, bias2, state, b), torch), moved, 8.0 * N * dh * dd * dv)
+        # the recurrence beside the attention: a state per channel and index (Mufotar) beside a state per head (Zepalorn)
+        x, dt = torch.randn(N, ci, device=dev).to(bf) * 0.5, torch.randn(N, ci, device=dev).to(bf)
+        bc, xz = torch.randn(N, rk + 2 * ns, device=dev).to(bf), torch.randn(N, 2 * ci, device=dev).to(bf)
+        A2, dtb, skip = torch.zeros(ci, ns, device=dev), torch.full((ci,), -3.0, device=dev), torch.ones(ci, device=dev)
+        st = torch.zeros(batch + 1, ci, ns, device=dev)
+        moved = batch * 2 * 4 * ci * ns + N * 2 * (4 * ci + 2 * ns)
+        out[f"selective_scan_{what}_mufotar"] = entry(_time_graph(lambda: K.selective_scan(x, dt, bc, rk, rk + ns, xz, ci, A2, dtb, skip, st, b), torch), moved, 6.0 * N * ci * ns)
+        sh, sv, sn = ci // 64, 64, 128
+        xbc, dth = torch.randn(N, sh * sv + 2 * sn, device=dev).to(bf) * 0.5, torch.randn(N, sh, device=dev).to(bf)
+        A3, b3, k3 = torch.zeros(sh, device=dev), torch.full((sh,), -3.0, device=dev), torch.ones(sh, device=dev)
+        st3 = torch.zeros(batch + 1, sh, sv, sn, device=dev)
+        moved = batch * 2 * 4 * sh * sn * sv + N * (2 * (sh * sv + 2 * sn) + 4 * sh * sv)
+        out[f"state_space_{what}_zepalorn"] = entry(_time_graph(lambda: K.ssm_scan(xbc, sh, 1, sn, sv, dth, 0, A3, b3, k3, st3, b), torch), moved, 6.0 * N * sh * sn * sv)
+        # the feed-forward: router, sort by expert, the experts' two grouped products and the weighted sum (Mufotar) beside a dense
+        # gated unit with as many rows of weights as a token's chosen experts have (Zepalorn)
+        h = torch.randn(N, W, device=dev).to(bf)
+        w_router, corr = torch.randn(E + ident, W, device=dev).to(bf) * 0.05, torch.zeros(E + ident, device=dev)
+        wgu, wdn = torch.randn(E, 2 * eff, W, device=dev).to(bf) * 0.02, torch.randn(E, W, eff, device=dev).to(bf) * 0.02
+        y = torch.zeros(N, W, device=dev)
+        ids, wts = K.moe_route(K.linear(h, w_router, out_dtype=torch.float32), corr, top)
+        real = int((ids < E).sum())
+        used = int(torch.unique(ids[ids < E]).numel())
+        fl = 6.0 * real * W * eff
+        moved = used * 3 * eff * W * 2 + N * W * (2 + 4)
+        out[f"router_{what}_mufotar"] = entry(_time_graph(lambda: K.moe_route(K.linear(h, w_router, out_dtype=torch.float32), corr, top), torch), N * W * 2 + (E + ident) * W * 2)
+        out[f"experts_{what}_mufotar"] = entry(_time_graph(lambda: K.moe_experts(h, ids, wts, wgu, wdn, add_to=y), torch), moved, fl)
+        wd_gu, wd_dn = torch.randn(2 * top * eff, W, device=dev).to(bf) * 0.02, torch.randn(W, top * eff, device=dev).to(bf) * 0.02
+        out[f"dense_unit_{what}_zepalorn"] = entry(_time_graph(lambda: K.linear(K.gate_up_act(h, wd_gu, bf, glu=(7.0, 1.702, 1.0)), wd_dn, add_to=y), torch),
+                                                   3 * top * eff * W * 2 + N * W * (2 + 4), 6.0 * N * top * W * eff)
+        del wgu, wdn, wd_gu, wd_dn
+    # norms, the join of the two mixers, the cap on the logits, at 2,048 rows
+    N = 2048
+    res, w, bb = torch.randn(N, W, device=dev), torch.ones(W, device=dev), torch.zeros(W, device=dev)
+    out["layernorm_bias_mufotar"] = entry(_time_graph(lambda: K.layernorm(res, w, 1e-6, bf, bias=bb), torch), N * W * (4 + 2))
+    out["layernorm_zepalorn"] = entry(_time_graph(lambda: K.layernorm(res, w, 1e-6, bf), torch), N * W * (4 + 2))
+    a2, b2, y = torch.randn(N, W, device=dev), torch.randn(N, W, device=dev), torch.zeros(N, W, device=dev)
+    out["weighted_pair_mufotar"] = entry(_time_graph(lambda: K.weighted_pair(a2, b2, 1.2, 0.9, y), torch), N * W * (4 + 4 + 4 + 4))
+    out["mean_of_two_zepalorn"] = entry(_time_graph(lambda: K.dual_rmsnorm_mix(a2, b2, w, w, 1e-6, 0.5, y), torch), N * W * (4 + 4 + 4 + 4))
+    o, g, nw = torch.randn(N, dh * dv, device=dev), torch.randn(N, dh * dv, device=dev).to(bf), torch.ones(dv, device=dev)
+    out["gated_norm_silu_mufotar"] = entry(_time_graph(lambda: K.group_rmsnorm_gate(o, g, 0, nw, dv, 1e-6, False, bf, gate_act="silu"), torch), N * dh * dv * (4 + 2 + 2))
+    out["gated_norm_zepalorn"] = entry(_time_graph(lambda: K.group_rmsnorm_gate(o, g, 0, nw, dv, 1e-6, False, bf), torch), N * dh * dv * (4 + 2 + 2))
+    lg = torch.randn(64, 32768, device=dev)
+    out["softcap_mufotar"] = entry(_time_graph(lambda: K.softcap(lg, 30.0), torch), 64 * 32768 * 8)
+    K.check_device_errors()
+    return out
+
+
+def mufotar_workload(a) -> int:
+    import torch
+
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    steps = min(a.steps, 256)
+    for size in MUFOTAR_SIZES:
+        W, E, ident, top, eff = (MUFOTAR_SIZES[size][i] for i in (0, 11, 12, 13, 14))
+        layers, vocab = MUFOTAR_SIZES[size][-2:]
+        row = {}
+        for name, config in (("mufotar", mufotar_config(size)), ("zepalorn", zepalorn_beside_mufotar(size))):
+            with tempfile.TemporaryDirectory() as tmp:
+                folder = write_random_model(config, Path(tmp) / "model", seed=0, store_dtype="bfloat16")
+                pt = model_points(folder, vocab, a.batch, a.context or 4096, a.prefill_tokens, steps, max(a.warmup, 3), torch)
+            if name == "mufotar":   # a step reads at most batch * top of a layer's experts: the others' matrices are taken off the bytes
+                own = sum(1 for lc in config["layers"] if lc["mlp"]["kind"] == "moe" and "weights_of" not in lc)
+                pt["decode_bytes"] -= own * max(0, E - a.batch * top) * 3 * eff * W * 2
+            pt["decode_frac_of_copy_peak"] = round(pt["decode_bytes"] / (pt["decode_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            row[name] = pt
+        sizes[size] = row
+    line = {"metric": f"Mufotar beside Zepalorn of equal size: decode (batch {a.batch}, context {a.context or 4096}) and prefill ({a.prefill_tokens} tokens), bf16, random weights",
+            "unit": "ms and tokens/s per size", "n_gpus": 1, "impl": "ours", "dtype": "bf16", "steps": steps, "warmup": max(a.warmup, 3),
+            "data": "synthetic: random weights (seed 0), uniform random token ids, synthetic cache contents",
+            "config": {"sizes": {k: dict(zip(MUFOTAR_NAMES, v)) for k, v in MUFOTAR_SIZES.items()}, "block_size": BLOCK, "peaks": pk["source"],
+                       "l2": "weights + cache per step larger than L2, no flush"},
+            "clocks": sampler.stop(), "sizes": sizes}
+    if a.kernels:
+        line["kernels"] = mufotar_kernel_points(torch, pk)
+    print(json.dumps(line))
+    return 0
+
+
 def luvutar_workload(a) -> int:
     import torch
 
@@ -991,10 +1170,11 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="measure one part only (for profiling); the JSON line then lacks the rest")
-    ap.add_argument("--workload", default="steps", choices=["steps", "serving", "luvutar", "zepalorn"],
+    ap.add_argument("--workload", default="steps", choices=["steps", "serving", "luvutar", "zepalorn", "mufotar"],
                     help="serving: continuous batching of --requests requests (prompts U[128,2048], outputs U[64,512]) through Engine; "
-                         "luvutar, zepalorn: that decoder at two layer sizes beside the Qwen2 decoder of equal size (decode and prefill)")
-    ap.add_argument("--kernels", action="store_true", help="luvutar, zepalorn: also time its kernels one by one beside their Qwen2 counterparts")
+                         "luvutar, zepalorn: that decoder at two layer sizes beside the Qwen2 decoder of equal size (decode and prefill); "
+                         "mufotar: that decoder at two layer sizes beside the Zepalorn decoder of equal size")
+    ap.add_argument("--kernels", action="store_true", help="luvutar, zepalorn, mufotar: also time its kernels one by one beside their counterparts")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--token-budget", type=int, default=2048, help="serving: tokens per step (max_num_batched_tokens)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt")
@@ -1008,6 +1188,8 @@ def main() -> int:
         return luvutar_workload(a)
     if a.workload == "zepalorn":
         return zepalorn_workload(a)
+    if a.workload == "mufotar":
+        return mufotar_workload(a)
     PREFILL_TOKENS = a.prefill_tokens
     shape_name, changes, shape_context = SHAPES[a.shape]
     MODEL.update(changes)

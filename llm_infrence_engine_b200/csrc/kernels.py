@@ -59,6 +59,7 @@ class CudaKernels:
         self.use_cluster_gate_up = False  # ... by pairs of blocks that share their weight rows (TMA multicast within a cluster of two)
         self.use_pair_gate_up = True     # ... by pairs of multiprocessors on tiles of 256 rows (tcgen05 cta_group::2) ...
         self.pair_gate_up_min_rows = 1024  # ... from this many rows on (measured: 3 to 8 % faster at 2,048 rows, 5 % slower at 512)
+        self.use_tc_experts = True     # routed experts with many rows per expert: both grouped products on tcgen05 (bfloat16)
         self.use_tc_gate_up = True     # prompt portions: gate/up product with the activation as its epilogue, one tcgen05 kernel
         self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel ...
         self.tc_qkv_min_rows = 2048    # ... from this many rows on: below, the library product + the rotation kernel are 4 to 10 % of a step faster
@@ -106,7 +107,7 @@ class CudaKernels:
                    "llmie_layernorm", "llmie_group_rmsnorm_gate", "llmie_dual_rmsnorm_mix", "llmie_glu_clamped", "llmie_qk_norm_rope_store",
                    "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan", "llmie_zero_fresh_states",
                    "llmie_selective_scan", "llmie_weighted_pair", "llmie_moe_route", "llmie_moe_sort", "llmie_moe_gemm", "llmie_moe_combine",
-                   "llmie_moe_tile_rows"):
+                   "llmie_moe_tile_rows", "llmie_moe_gather", "llmie_moe_grouped_tc", "llmie_moe_grouped_tc_rows"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = self._gate_up_glu_pair = None
@@ -1372,18 +1373,35 @@ class CudaKernels:
             raise KernelError("moe_experts: the matrices, the choices and the rows do not fit each other")
         dev = h.device
         pairs = N * top
-        tile_rows = self.lib.llmie_moe_tile_rows()
+        dt = self._dt(h, "h")
+        rows = min(self.lib.llmie_moe_tile_rows(K), self.lib.llmie_moe_tile_rows(F))
+        # more than two rows per expert on average: the tensor cores, which fetch an expert's matrices once for up to 128 rows (the
+        # CUDA-core product fetches them once per tile of at most 8; with one or two rows per expert both wait on the same bytes, and
+        # the CUDA-core product spreads them over more blocks). The choice looks at sizes only, never at a count on the device
+        tc = self.use_tc_experts and h.dtype == torch.bfloat16 and K % 8 == 0 and F % 8 == 0 and pairs > 2 * E
+        if not tc and rows < 1:
+            raise KernelError(f"moe_experts: rows of {max(K, F)} numbers do not fit the shared memory of the product for few rows")
+        tile_rows = self.lib.llmie_moe_grouped_tc_rows() if tc else rows
         max_tiles = -(-pairs // tile_rows) + E
         book = torch.empty((E + 1 + 2 * pairs + 1 + 2 * max_tiles,), dtype=torch.int32, device=dev)
         offsets, perm, place_of, tiles = book[:E + 1], book[E + 1:E + 1 + pairs], book[E + 1 + pairs:E + 1 + 2 * pairs], book[E + 1 + 2 * pairs:]
-        self._check(self.lib.llmie_moe_sort(_ptr(ids), pairs, E, _ptr(offsets), _ptr(perm), _ptr(place_of), _ptr(tiles), max_tiles, self._stream()), "moe_experts (sort)")
-        dt = self._dt(h, "h")
+        self._check(self.lib.llmie_moe_sort(_ptr(ids), pairs, E, tile_rows, _ptr(offsets), _ptr(perm), _ptr(place_of), _ptr(tiles), max_tiles,
+                                            self._stream()), "moe_experts (sort)")
         act = torch.empty((pairs, F), dtype=h.dtype, device=dev)
-        self._check(self.lib.llmie_moe_gemm(_ptr(h), _ptr(perm), top, _ptr(w_gate_up), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(act), F, K, 1, dt,
-                                            self._stream()), "moe_experts (gate and up)")
         y = torch.empty((pairs, K), dtype=torch.float32, device=dev)
-        self._check(self.lib.llmie_moe_gemm(_ptr(act), _ptr(None), 1, _ptr(w_down), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(y), K, F, 0, dt,
-                                            self._stream()), "moe_experts (down)")
+        if tc:
+            xs = torch.empty((pairs, K), dtype=h.dtype, device=dev)
+            err = _ptr(self._errors(dev))
+            self._check(self.lib.llmie_moe_gather(_ptr(h), _ptr(perm), _ptr(offsets), E, top, _ptr(xs), pairs, K, self._stream()), "moe_experts (gather)")
+            self._check(self.lib.llmie_moe_grouped_tc(_ptr(xs), pairs, _ptr(w_gate_up), E, _ptr(offsets), _ptr(tiles), max_tiles, _ptr(act), F, K, 1,
+                                                      self.num_sms, err, self._stream()), "moe_experts (gate and up, tcgen05)")
+            self._check(self.lib.llmie_moe_grouped_tc(_ptr(act), pairs, _ptr(w_down), E, _ptr(offsets), _ptr(tiles), max_tiles, _ptr(y), K, F, 0,
+                                                      self.num_sms, err, self._stream()), "moe_experts (down, tcgen05)")
+        else:
+            self._check(self.lib.llmie_moe_gemm(_ptr(h), _ptr(perm), top, _ptr(w_gate_up), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(act), F, K, 1,
+                                                tile_rows, dt, self._stream()), "moe_experts (gate and up)")
+            self._check(self.lib.llmie_moe_gemm(_ptr(act), _ptr(None), 1, _ptr(w_down), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(y), K, F, 0,
+                                                tile_rows, dt, self._stream()), "moe_experts (down)")
         self._check(self.lib.llmie_moe_combine(_ptr(add_to), _ptr(y), _ptr(h), _ptr(place_of), _ptr(weights), N, top, K, dt, self._stream()),
                     "moe_experts (sum)")
         self._unfresh(add_to)

@@ -13,9 +13,9 @@
 namespace {
 
 constexpr int ROUTE_MAX_PER_LANE = 16;   // up to 512 router outputs
-constexpr int MOE_TM = 32;               // rows of a tile of the grouped product
-constexpr int MOE_TN = 64;
-constexpr int MOE_TK = 16;
+constexpr int MOE_TM = 8;                // most rows of a tile of the grouped product on the CUDA cores
+constexpr int MOE_COLS = 32;             // outputs per block there
+constexpr int MOE_ROWS_SMEM = 96 * 1024; // what a tile's rows may take of shared memory
 constexpr int SORT_THREADS = 1024;
 constexpr int SORT_MAX_EXPERTS = 4096;
 
@@ -133,89 +133,165 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const int* __res
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
-// The grouped product on the CUDA cores, one tile of MOE_TM places x MOE_TN outputs per block, the tile's expert from the list.
+// The grouped product on the CUDA cores for FEW rows per expert (decode steps) and for float32: a tile is up to `tile_rows` (at
+// most MOE_TM) places of one expert, whose rows of K numbers lie in shared memory as floats; a block owns MOE_COLS outputs, a warp
+// MOE_COLS / 8 of them, taken together: the lanes walk the outputs' weight rows (and, GATED, the up rows of the same outputs)
+// 16 bytes at a time, so the matrices are read once per tile in full lines, which is what bounds a decode step.
 //   GATED: out[place, j] = silu(a . Wg[e][j]) * (a . Wu[e][j]) with W [E][2 F][K] (an expert's gate rows, then its up rows), out of type TO
 //   else:  out[place, j] = a . W[e][j] with W [E][F][K]
 // The row a of a place is x[row_map[place] / row_div] (the token of the pair that sits there), or x[place] without a map.
+// A sum runs over K in one order whatever the tile holds: a place's result does not depend on its neighbours.
 template <typename T, typename TO, bool GATED>
-__global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ x, const int* __restrict__ row_map, int row_div, const T* __restrict__ w,
+__global__ void __launch_bounds__(256) moe_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_map, int row_div, const T* __restrict__ w,
                                                        const int* __restrict__ offsets, const int* __restrict__ tiles, TO* __restrict__ out, int F,
-                                                       int K) {
-    __shared__ float a_s[MOE_TK][MOE_TM + 1];
-    __shared__ float b_s[GATED ? 2 : 1][MOE_TK][MOE_TN + 1];
-    __shared__ int rows_s[MOE_TM];
+                                                       int K, int tile_rows) {
+    extern __shared__ __align__(16) float moe_rows_smem[];   // [tile_rows][K]
+    constexpr int VN = Vec16<T>::N;
     pdl_trigger();
     pdl_wait();
     if ((int)blockIdx.y >= tiles[0]) return;
     const int e = tiles[1 + 2 * blockIdx.y], p0 = tiles[2 + 2 * blockIdx.y];
-    const int p_end = min(offsets[e + 1], p0 + MOE_TM);
-    const int n0 = blockIdx.x * MOE_TN;
-    if (threadIdx.x < MOE_TM) {
-        const int p = p0 + threadIdx.x;
-        rows_s[threadIdx.x] = p < p_end ? (row_map ? row_map[p] / row_div : p) : -1;
+    const int count = min(offsets[e + 1] - p0, tile_rows);
+    const bool vec = (K % VN) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+    for (int r = 0; r < count; ++r) {
+        const int p = p0 + r;
+        const T* src = x + (size_t)(row_map ? row_map[p] / row_div : p) * K;
+        float* dst = moe_rows_smem + (size_t)r * K;
+        if (vec) {
+            for (int k = threadIdx.x * VN; k < K; k += 256 * VN) {
+                float v[VN];
+                Vec16<T>::load(src + k, v);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) dst[k + i] = v[i];
+            }
+        } else {
+            for (int k = threadIdx.x; k < K; k += 256) dst[k] = to_f32(src[k]);
+        }
     }
     __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T* we = w + (size_t)e * (GATED ? 2 : 1) * F * K;
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // outputs 4 tx .. 4 tx + 3 of places 2 ty, 2 ty + 1
-    float acc[GATED ? 2 : 1][2][4] = {};
-    for (int k0 = 0; k0 < K; k0 += MOE_TK) {
-        for (int i = threadIdx.x; i < MOE_TM * MOE_TK; i += 256) {
-            const int m = i / MOE_TK, k = i % MOE_TK;
-            const int r = rows_s[m];
-            a_s[k][m] = (r >= 0 && k0 + k < K) ? to_f32(x[(size_t)r * K + k0 + k]) : 0.f;
-        }
-        for (int i = threadIdx.x; i < MOE_TN * MOE_TK; i += 256) {
-            const int n = i / MOE_TK, k = i % MOE_TK;
-            const bool in = n0 + n < F && k0 + k < K;
-            b_s[0][k][n] = in ? to_f32(we[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
-            if (GATED) b_s[GATED ? 1 : 0][k][n] = in ? to_f32(we[(size_t)(F + n0 + n) * K + k0 + k]) : 0.f;
-        }
-        __syncthreads();
+    constexpr int CPW = MOE_COLS / 8;   // a warp's outputs, taken together: their weight rows are in flight at once
+    const int j0 = blockIdx.x * MOE_COLS + warp * CPW;
+    if (j0 >= F) return;
+    const T* wrow[CPW];
 #pragma unroll
-        for (int k = 0; k < MOE_TK; ++k) {
-            const float a0 = a_s[k][2 * ty], a1 = a_s[k][2 * ty + 1];
+    for (int c = 0; c < CPW; ++c) wrow[c] = we + (size_t)min(j0 + c, F - 1) * K;   // (an output past the end repeats the last: not stored)
+    const size_t up = (size_t)F * K;   // from an output's gate row to its up row (read only when GATED)
+    float ag[CPW][MOE_TM] = {}, au[GATED ? CPW : 1][MOE_TM] = {};
+    if (vec) {
+        for (int k = lane * VN; k < K; k += 32 * VN) {
+            float g[CPW][VN], u[GATED ? CPW : 1][VN];
 #pragma unroll
-            for (int h = 0; h < (GATED ? 2 : 1); ++h) {
+            for (int c = 0; c < CPW; ++c) {
+                Vec16<T>::load(wrow[c] + k, g[c]);
+                if (GATED) Vec16<T>::load(wrow[c] + up + k, u[GATED ? c : 0]);
+            }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float b = b_s[h][k][4 * tx + j];
-                    acc[h][0][j] = fmaf(a0, b, acc[h][0][j]);
-                    acc[h][1][j] = fmaf(a1, b, acc[h][1][j]);
+            for (int r = 0; r < MOE_TM; ++r) {
+                if (r < count) {
+                    const float* a = moe_rows_smem + (size_t)r * K + k;
+#pragma unroll
+                    for (int i = 0; i < VN; i += 4) {
+                        const float4 av = *reinterpret_cast<const float4*>(a + i);
+#pragma unroll
+                        for (int c = 0; c < CPW; ++c) {
+                            ag[c][r] = fmaf(av.x, g[c][i], ag[c][r]); ag[c][r] = fmaf(av.y, g[c][i + 1], ag[c][r]);
+                            ag[c][r] = fmaf(av.z, g[c][i + 2], ag[c][r]); ag[c][r] = fmaf(av.w, g[c][i + 3], ag[c][r]);
+                            if (GATED) {
+                                float& s = au[GATED ? c : 0][r];
+                                s = fmaf(av.x, u[GATED ? c : 0][i], s); s = fmaf(av.y, u[GATED ? c : 0][i + 1], s);
+                                s = fmaf(av.z, u[GATED ? c : 0][i + 2], s); s = fmaf(av.w, u[GATED ? c : 0][i + 3], s);
+                            }
+                        }
+                    }
                 }
             }
         }
-        __syncthreads();
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            float g[CPW], u[GATED ? CPW : 1];
+#pragma unroll
+            for (int c = 0; c < CPW; ++c) {
+                g[c] = to_f32(wrow[c][k]);
+                if (GATED) u[GATED ? c : 0] = to_f32(wrow[c][up + k]);
+            }
+#pragma unroll
+            for (int r = 0; r < MOE_TM; ++r) {
+                if (r < count) {
+                    const float a = moe_rows_smem[(size_t)r * K + k];
+#pragma unroll
+                    for (int c = 0; c < CPW; ++c) {
+                        ag[c][r] = fmaf(a, g[c], ag[c][r]);
+                        if (GATED) au[GATED ? c : 0][r] = fmaf(a, u[GATED ? c : 0], au[GATED ? c : 0][r]);
+                    }
+                }
+            }
+        }
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int p = p0 + 2 * ty + i;
-        if (p >= p_end) continue;
+    for (int r = 0; r < MOE_TM; ++r) {
+        if (r < count) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int n = n0 + 4 * tx + j;
-            if (n >= F) continue;
-            const float v = GATED ? silu_f(acc[0][i][j]) * acc[GATED ? 1 : 0][i][j] : acc[0][i][j];
-            out[(size_t)p * F + n] = from_f32<TO>(v);
+            for (int c = 0; c < CPW; ++c) {
+                const float sg = warp_sum(ag[c][r]);
+                const float su = GATED ? warp_sum(au[GATED ? c : 0][r]) : 0.f;
+                if (lane == 0 && j0 + c < F) out[(size_t)(p0 + r) * F + j0 + c] = from_f32<TO>(GATED ? silu_f(sg) * su : sg);
+            }
         }
     }
 }
 
+// xs[place] = x[perm[place] / top] for the places that the sort filled (offsets[E] of them): the rows of the tokens, in the order
+// of their experts, as the tensor-core grouped product reads them. One block per place.
+__global__ void moe_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ perm, const int* __restrict__ offsets, int E, int top,
+                                  bf16* __restrict__ xs, int K) {
+    pdl_trigger();
+    pdl_wait();
+    const int p = blockIdx.x;
+    if (p >= offsets[E]) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(perm[p] / top) * K);
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)p * K);
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+}
+
 // residual[t] += sum_k weight[t, k] * (y[place_of[t, k]] for an expert with matrices, h[t] itself for an identity expert), the
-// experts of a token in the order of its choice. One block per token.
-template <typename T>
-__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ y, const T* __restrict__ h, const int* __restrict__ place_of,
-                                   const float* __restrict__ weights, int top, int W) {
+// experts of a token in the order of its choice. Block (t, c): COMBINE_VEC columns per thread of token t from column
+// c * blockDim.x * COMBINE_VEC on; the rows of a token's experts are fetched side by side (COMBINE_VEC 4: rows of 16-byte pieces).
+template <typename T, int COMBINE_VEC>
+__global__ void __launch_bounds__(256) moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ y, const T* __restrict__ h,
+                                                          const int* __restrict__ place_of, const float* __restrict__ weights, int top, int W) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float sum = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int p = place_of[(size_t)t * top + k];
-            const float v = p >= 0 ? y[(size_t)p * W + i] : to_f32(h[(size_t)t * W + i]);
-            sum = fmaf(weights[(size_t)t * top + k], v, sum);
+    const int i = (blockIdx.y * blockDim.x + threadIdx.x) * COMBINE_VEC;
+    if (i >= W) return;
+    float sum[COMBINE_VEC] = {};
+    for (int k = 0; k < top; ++k) {
+        const int p = place_of[(size_t)t * top + k];
+        const float wk = weights[(size_t)t * top + k];
+        float v[COMBINE_VEC];
+        if (p >= 0) {
+            if (COMBINE_VEC == 4) {
+                const float4 q = *reinterpret_cast<const float4*>(y + (size_t)p * W + i);
+                v[0] = q.x; v[1 % COMBINE_VEC] = q.y; v[2 % COMBINE_VEC] = q.z; v[3 % COMBINE_VEC] = q.w;
+            } else {
+                v[0] = y[(size_t)p * W + i];
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < COMBINE_VEC; ++j) v[j] = to_f32(h[(size_t)t * W + i + j]);
         }
-        residual[(size_t)t * W + i] += sum;
+#pragma unroll
+        for (int j = 0; j < COMBINE_VEC; ++j) sum[j] = fmaf(wk, v[j], sum[j]);
+    }
+    float* r = residual + (size_t)t * W + i;
+    if (COMBINE_VEC == 4) {
+        float4 q = *reinterpret_cast<float4*>(r);
+        q.x += sum[0]; q.y += sum[1 % COMBINE_VEC]; q.z += sum[2 % COMBINE_VEC]; q.w += sum[3 % COMBINE_VEC];
+        *reinterpret_cast<float4*>(r) = q;
+    } else {
+        r[0] += sum[0];
     }
 }
 
@@ -227,34 +303,73 @@ LLMIE_API int llmie_moe_route(const float* logits, const float* correction, int*
     return launch_kernel(moe_route_kernel, dim3((N + 3) / 4), dim3(128), 0, s, logits, correction, ids, weights, N, total, top);
 }
 
-LLMIE_API int llmie_moe_tile_rows() { return MOE_TM; }
-
-LLMIE_API int llmie_moe_sort(const int* ids, int pairs, int E, int* offsets, int* perm, int* place_of, int* tiles, int max_tiles, cudaStream_t s) {
-    if (pairs <= 0) return 0;
-    if (E <= 0 || E > SORT_MAX_EXPERTS || max_tiles <= 0) return LLMIE_ERR_BAD_ARGUMENT;
-    return launch_kernel(moe_sort_kernel, dim3(1), dim3(SORT_THREADS), 0, s, ids, pairs, E, MOE_TM, offsets, perm, place_of, tiles, max_tiles);
+// Rows per tile of the grouped product on the CUDA cores for rows of K numbers: as many as fit the shared memory, at most MOE_TM;
+// 0: the rows are too long for it.
+LLMIE_API int llmie_moe_tile_rows(int K) {
+    if (K <= 0) return 0;
+    const long long fit = MOE_ROWS_SMEM / ((long long)K * 4);
+    return (int)(fit > MOE_TM ? MOE_TM : fit);
 }
 
-// gated != 0: w [E][2 F][K], out [places][F] of the storage type; else w [E][F][K], out [places][F] float.
-LLMIE_API int llmie_moe_gemm(const void* x, const int* row_map, int row_div, const void* w, const int* offsets, const int* tiles, int max_tiles,
-                             void* out, int F, int K, int gated, int dtype, cudaStream_t s) {
-    if (max_tiles <= 0) return 0;
-    if (F <= 0 || K <= 0 || max_tiles > 65535 || (row_map && row_div <= 0)) return LLMIE_ERR_BAD_ARGUMENT;
-    const dim3 grid((F + MOE_TN - 1) / MOE_TN, max_tiles);
-    if (dtype == DT_F32) {
-        if (gated) return launch_kernel(moe_gemm_kernel<float, float, true>, grid, dim3(256), 0, s, (const float*)x, row_map, row_div, (const float*)w, offsets, tiles, (float*)out, F, K);
-        return launch_kernel(moe_gemm_kernel<float, float, false>, grid, dim3(256), 0, s, (const float*)x, row_map, row_div, (const float*)w, offsets, tiles, (float*)out, F, K);
+// tile_rows: the most places of a tile (what the product that follows wants: llmie_moe_tile_rows(K), or 128 for the tensor cores).
+LLMIE_API int llmie_moe_sort(const int* ids, int pairs, int E, int tile_rows, int* offsets, int* perm, int* place_of, int* tiles, int max_tiles,
+                             cudaStream_t s) {
+    if (pairs <= 0) return 0;
+    if (E <= 0 || E > SORT_MAX_EXPERTS || max_tiles <= 0 || tile_rows <= 0) return LLMIE_ERR_BAD_ARGUMENT;
+    return launch_kernel(moe_sort_kernel, dim3(1), dim3(SORT_THREADS), 0, s, ids, pairs, E, tile_rows, offsets, perm, place_of, tiles, max_tiles);
+}
+
+template <typename T, typename TO, bool GATED>
+static int launch_moe_rows(const void* x, const int* row_map, int row_div, const void* w, const int* offsets, const int* tiles, int max_tiles, void* out,
+                           int F, int K, int tile_rows, cudaStream_t s) {
+    const size_t smem = (size_t)tile_rows * K * sizeof(float);
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(moe_rows_kernel<T, TO, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_ROWS_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        allowed = MOE_ROWS_SMEM;
     }
-    if (gated) return launch_kernel(moe_gemm_kernel<bf16, bf16, true>, grid, dim3(256), 0, s, (const bf16*)x, row_map, row_div, (const bf16*)w, offsets, tiles, (bf16*)out, F, K);
-    return launch_kernel(moe_gemm_kernel<bf16, float, false>, grid, dim3(256), 0, s, (const bf16*)x, row_map, row_div, (const bf16*)w, offsets, tiles, (float*)out, F, K);
+    const dim3 grid((F + MOE_COLS - 1) / MOE_COLS, max_tiles);
+    return launch_kernel(moe_rows_kernel<T, TO, GATED>, grid, dim3(256), smem, s, (const T*)x, row_map, row_div, (const T*)w, offsets, tiles, (TO*)out, F, K,
+                         tile_rows);
+}
+
+// gated != 0: w [E][2 F][K], out [places][F] of the storage type; else w [E][F][K], out [places][F] float. tile_rows as given to the sort.
+LLMIE_API int llmie_moe_gemm(const void* x, const int* row_map, int row_div, const void* w, const int* offsets, const int* tiles, int max_tiles,
+                             void* out, int F, int K, int gated, int tile_rows, int dtype, cudaStream_t s) {
+    if (max_tiles <= 0) return 0;
+    if (F <= 0 || K <= 0 || max_tiles > 65535 || (row_map && row_div <= 0) || tile_rows <= 0 || tile_rows > MOE_TM || tile_rows > llmie_moe_tile_rows(K))
+        return LLMIE_ERR_BAD_ARGUMENT;
+    if (dtype == DT_F32) {
+        if (gated) return launch_moe_rows<float, float, true>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, s);
+        return launch_moe_rows<float, float, false>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, s);
+    }
+    if (gated) return launch_moe_rows<bf16, bf16, true>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, s);
+    return launch_moe_rows<bf16, float, false>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, s);
+}
+
+// xs [pairs][K] bfloat16 (K a multiple of 8, 16-byte aligned rows): the tokens' rows in the order of the sort.
+LLMIE_API int llmie_moe_gather(const void* x, const int* perm, const int* offsets, int E, int top, void* xs, int pairs, int K, cudaStream_t s) {
+    if (pairs <= 0) return 0;
+    if (K <= 0 || K % 8 || top <= 0 || ((uintptr_t)x & 15) || ((uintptr_t)xs & 15)) return LLMIE_ERR_BAD_ARGUMENT;
+    return launch_kernel(moe_gather_kernel, dim3(pairs), dim3(K / 8 < 256 ? (K / 8 < 32 ? 32 : K / 8) : 256), 0, s, (const bf16*)x, perm, offsets, E, top,
+                         (bf16*)xs, K);
 }
 
 LLMIE_API int llmie_moe_combine(float* residual, const float* y, const void* h, const int* place_of, const float* weights, int N, int top, int W,
                                 int dtype, cudaStream_t s) {
     if (N <= 0) return 0;
     if (top <= 0 || W <= 0) return LLMIE_ERR_BAD_ARGUMENT;
+    const bool vec = W % 4 == 0 && (((uintptr_t)residual | (uintptr_t)y) & 15) == 0;
+    const int per = vec ? 4 : 1;
     int threads = 32;
-    while (threads < 256 && threads * 2 <= W) threads *= 2;
-    if (dtype == DT_F32) return launch_kernel(moe_combine_kernel<float>, dim3(N), dim3(threads), 0, s, residual, y, (const float*)h, place_of, weights, top, W);
-    return launch_kernel(moe_combine_kernel<bf16>, dim3(N), dim3(threads), 0, s, residual, y, (const bf16*)h, place_of, weights, top, W);
+    while (threads < 256 && threads * per < W) threads *= 2;
+    const dim3 grid(N, (W + threads * per - 1) / (threads * per));
+    if (grid.y > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    if (dtype == DT_F32) {
+        if (vec) return launch_kernel(moe_combine_kernel<float, 4>, grid, dim3(threads), 0, s, residual, y, (const float*)h, place_of, weights, top, W);
+        return launch_kernel(moe_combine_kernel<float, 1>, grid, dim3(threads), 0, s, residual, y, (const float*)h, place_of, weights, top, W);
+    }
+    if (vec) return launch_kernel(moe_combine_kernel<bf16, 4>, grid, dim3(threads), 0, s, residual, y, (const bf16*)h, place_of, weights, top, W);
+    return launch_kernel(moe_combine_kernel<bf16, 1>, grid, dim3(threads), 0, s, residual, y, (const bf16*)h, place_of, weights, top, W);
 }

@@ -142,19 +142,31 @@ def gated_unit(h, t, p: str, act):
     return (act(h @ t[f"{p}.gate"].T) * (h @ t[f"{p}.up"].T)) @ t[f"{p}.down"].T
 
 
-def route(h, mlp: dict, t, p: str):
-    """(chosen experts [T, top], their weights [T, top]); experts from ``experts`` on are identity experts."""
+def route(h, mlp: dict, t, p: str, close_out: Optional[list] = None):
+    """(chosen experts [T, top], their weights [T, top]); experts from ``experts`` on are identity experts. ``close_out`` collects,
+    per token, whether the last score taken and the first one left out are nearly equal (within a few percent of what a
+    rounding of the input to 8 bits moves them by: a score s moves by about s * |dz|)."""
     r = mlp["router"]
-    s = torch.softmax(h @ t[f"{p}.router"].T, dim=-1)
+    z = h @ t[f"{p}.router"].T
+    s = torch.softmax(z, dim=-1)
     choice = s + t[f"{p}.correction"] if f"{p}.correction" in t else s
-    idx = torch.topk(choice, int(r["top"]), dim=-1).indices
+    top = int(r["top"])
+    idx = torch.topk(choice, top, dim=-1).indices
+    if close_out is not None:
+        if top < choice.shape[-1]:
+            order = torch.sort(choice, dim=-1, descending=True)
+            gap = order.values[:, top - 1] - order.values[:, top]
+            s_edge = torch.gather(s, 1, order.indices[:, top - 1:top + 1]).max(-1).values
+            close_out.append(gap < 0.03 * z.abs().max(-1).values.clamp(min=1.0) * s_edge)
+        else:
+            close_out.append(torch.zeros(h.shape[0], dtype=torch.bool))
     w = torch.gather(s, 1, idx)
     return idx, w / (w.sum(-1, keepdim=True) + 1e-20)
 
 
-def experts(h, mlp: dict, t, p: str):
+def experts(h, mlp: dict, t, p: str, close_out: Optional[list] = None):
     E = int(mlp["router"]["experts"])
-    idx, w = route(h, mlp, t, p)
+    idx, w = route(h, mlp, t, p, close_out)
     out = torch.zeros_like(h)
     for i in range(h.shape[0]):
         for e, we in zip(idx[i].tolist(), w[i]):
@@ -165,17 +177,19 @@ def experts(h, mlp: dict, t, p: str):
     return out
 
 
-def feed_forward(h, mlp: Optional[dict], t, p: str):
+def feed_forward(h, mlp: Optional[dict], t, p: str, close_out: Optional[list] = None):
     if mlp is None:
         return torch.zeros_like(h)
     if mlp.get("kind", "dense") == "dense":
         return gated_unit(h, t, p, gelu_tanh)
-    return experts(h, mlp, t, p)
+    return experts(h, mlp, t, p, close_out)
 
 
 # ------------------------------------------------------------------------------------------------------------ the model
-def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64, layers_out: Optional[list] = None):
-    """Logits ``[T, vocab]`` of one sequence. ``layers_out`` collects the residual stream after every layer."""
+def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64, layers_out: Optional[list] = None,
+            close_out: Optional[list] = None):
+    """Logits ``[T, vocab]`` of one sequence. ``layers_out`` collects the residual stream after every layer, ``close_out`` every
+    router's close calls (see ``route``)."""
     t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps = float(cfg["norm"]["eps"])
     x = t["embed"][torch.tensor(tokens, dtype=torch.long)]
@@ -189,7 +203,7 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], dtyp
             mix = parallel_mixer(h, layer["mixer"], t, f"{p}.mix", eps)
         else:
             raise ValueError(f"layer {i}: unknown type {layer['type']!r}")
-        x = x + (mix + feed_forward(h, layer.get("mlp"), t, f"{p}.mlp"))
+        x = x + (mix + feed_forward(h, layer.get("mlp"), t, f"{p}.mlp", close_out))
         if layers_out is not None:
             layers_out.append(x.clone())
     h = layer_norm(x, t["final.norm"], t["final.norm.b"], eps)
