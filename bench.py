@@ -965,7 +965,7 @@ def mufotar_config(size: str) -> dict:
     W, dh, dg, dd, dv, H, G, d, ci, ns, rk, E, ident, top, eff, sff, ff, layers, vocab = MUFOTAR_SIZES[size]
     moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "identity": ident, "top": top}, "shared": {"ff": sff}}
     delta = {"heads": dh, "kv_heads": dg, "dim": dd, "vdim": dv, "conv": 4}
-    pair = {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": {"base": 250000.0, "dims": d}},
+    pair = {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": {"base": 100000.0, "dims": d}},
             "right": {"inner": ci, "state": ns, "dt_rank": rk, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}
     kinds = []
     for i in range(layers):
@@ -987,7 +987,7 @@ def zepalorn_beside_mufotar(size: str) -> dict:
     for i in range(layers):
         mlp = {"kind": "dense", "ff": ff if i % 4 == 0 else top * eff + sff, "limit": 7.0}
         if i % 4 == 2:
-            left = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "conv": 4, "rot": {"base": 250000.0, "dims": d}}
+            left = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "conv": 4, "rot": {"base": 100000.0, "dims": d}}
             right = {"heads": ci // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}
             kinds.append({"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp})
         else:

@@ -361,6 +361,9 @@ class CudaKernels:
             return self.linear_tc(x, w, out=self._transient(M, N, w.device), accumulate=True)
         if small and out_dtype == torch.float32:
             return self.linear_tc(x, w)
+        if bf16 and out_dtype == torch.float32 and self.use_tc_gemm and K % 8 == 0 and N <= 128:
+            # few outputs in 32-bit for many rows (a router's logits over a prompt portion): one tile of weight rows, a block per 64 rows
+            return self.linear_tc(x, w)
         if self.use_cublas and bf16 and out_dtype == torch.bfloat16:
             self.launches += 1
             return torch.nn.functional.linear(x, w)

@@ -54,7 +54,7 @@ def ragged(lens, slots):
 # kernels
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("C,NS,lens", [(384, 32, [37, 1, 9]), (100, 12, [3, 70]), (64, 16, [1, 1, 1]), (520, 64, [130]), (48, 130, [20, 5]), (36, 1, [2, 1]),
+@pytest.mark.parametrize("C,NS,lens", [(392, 24, [37, 1, 9]), (100, 12, [3, 70]), (64, 16, [1, 1, 1]), (520, 64, [130]), (48, 130, [20, 5]), (36, 1, [2, 1]),
                                        (8, 256, [1, 33])])
 def test_selective_scan(K, dtype, C, NS, lens):
     ref, T = TorchKernels(), TD[dtype]
