@@ -9,7 +9,8 @@
 //   GATED   a [places, K] (the tokens' rows, gathered into the order of the places), w [E][2 F][K] (an expert's gate rows, then
 //           its up rows): out[place, j] = silu(a . Wg[e][j]) * (a . Wu[e][j]) as bfloat16 [places, F]. The accumulator of a tile
 //           is 128 lanes x 256 columns of tensor memory (gate sums, then up sums of the same outputs), one MMA of N = 256.
-//   else    a [places, K], w [E][F][K]: out[place, j] = a . W[e][j] as float32 [places, F]. Accumulator 128 x 128.
+//   else    a [places, K], w [E][F][K]: out[place, j] = a . W[e][j] as float32 [places, F]. The tile is 256 outputs wide (two boxes
+//           of 128 weight rows, one MMA of N = 256 as well): with 128 the kernel waited on the operands' way from L2.
 //
 // The kernel is persistent (one block per multiprocessor walks tiles blockIdx.x, + gridDim.x, ...; nobody on the host knows how
 // many there are) and built like the gate/up kernel of the dense feed-forward: warp 0 one lane issues the TMA boxes of a K step
@@ -28,7 +29,8 @@ template <bool GATED>
 __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                                                                   const int* __restrict__ offsets, const int* __restrict__ tile_list, void* __restrict__ out_,
                                                                   int F, int K, int* error_flag) {
-    constexpr int ACC_COLS = GATED ? 2 * BN : BN;                 // columns of tensor memory per accumulator
+    constexpr int ACC_COLS = 2 * BN;                              // columns of tensor memory per accumulator
+    constexpr int TILE_N = GATED ? BN : 2 * BN;                   // outputs per tile
     constexpr int B_BYTES = ACC_COLS * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ unsigned char raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -41,7 +43,7 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_co
     volatile int* issued = abort_flag + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_tiles = (F + BN - 1) / BN, nkb = (K + BK - 1) / BK;
+    const int n_tiles = (F + TILE_N - 1) / TILE_N, nkb = (K + BK - 1) / BK;
     const int w_rows = GATED ? 2 * F : F;   // rows of one expert's matrix
 
     if (tid == 0) {
@@ -71,7 +73,7 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_co
             int g = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const int mi = t % m_tiles, n0 = (t / m_tiles) * BN;
+                const int mi = t % m_tiles, n0 = (t / m_tiles) * TILE_N;
                 const int e = tile_list[1 + 2 * mi], p0 = tile_list[2 + 2 * mi];
                 const int w0 = e * w_rows + n0;
                 for (int kb = 0; kb < nkb; ++kb, ++g) {
@@ -81,7 +83,8 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_co
                     mbar_expect_tx(full + s, STAGE_BYTES);
                     tma_load_2d(st, &tmap_a, kb * BK, p0, full + s);
                     tma_load_2d(st + A_BYTES, &tmap_w, kb * BK, w0, full + s);
-                    if (GATED) tma_load_2d(st + A_BYTES + B_BYTES / 2, &tmap_w, kb * BK, w0 + F, full + s);   // up rows of the same outputs
+                    // the second box: the up rows of the same outputs, or the next 128 outputs (rows past an expert's last are not stored)
+                    tma_load_2d(st + A_BYTES + B_BYTES / 2, &tmap_w, kb * BK, w0 + (GATED ? F : BN), full + s);
                     *issued = g + 1;
                 }
             }
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_co
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++i) {
             const int buf = i & 1;
-            const int mi = t % m_tiles, n0 = (t / m_tiles) * BN;
+            const int mi = t % m_tiles, n0 = (t / m_tiles) * TILE_N;
             const int e = tile_list[1 + 2 * mi], p0 = tile_list[2 + 2 * mi];
             const bool mine = p0 + row < offsets[e + 1];   // the place is one of this expert's
             ok = __all_sync(0xffffffffu, mbar_wait(acc_full + buf, (i >> 1) & 1, abort_flag, error_flag, 54));
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_co
             } else {
                 float* dst = reinterpret_cast<float*>(out_) + (size_t)(p0 + row) * F + n0;
 #pragma unroll 2
-                for (int c = 0; c < BN; c += 16) {
+                for (int c = 0; c < TILE_N; c += 16) {
                     uint32_t v[16];
                     tmem_ld16(base + c, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
@@ -191,14 +194,14 @@ int launch_grouped(const bf16* a, int places, const bf16* w, int E, const int* o
     if (rc) return rc;
     rc = tensor_map(w, E * (GATED ? 2 : 1) * F, K, BN, &mw);
     if (rc) return rc;
-    constexpr size_t smem = (size_t)STAGES * (A_BYTES + (GATED ? 2 : 1) * BN * BK * 2) + 1024 + 256;
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + 2 * BN * BK * 2) + 1024 + 256;
     static bool set = false;
     if (!set) {
         cudaError_t e = cudaFuncSetAttribute(moe_grouped_tc_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
-    const long long most = (long long)max_tiles * ((F + BN - 1) / BN);
+    const long long most = (long long)max_tiles * ((F + (GATED ? BN : 2 * BN) - 1) / (GATED ? BN : 2 * BN));
     const int grid = (int)(most < num_blocks ? most : num_blocks);
     return launch_kernel(moe_grouped_tc_kernel<GATED>, dim3(grid), dim3(THREADS), smem, s, ma, mw, offsets, tile_list, out, F, K, error_flag);
 }
