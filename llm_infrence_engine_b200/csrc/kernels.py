@@ -1379,7 +1379,7 @@ class CudaKernels:
         dt = self._dt(h, "h")
         rows = min(self.lib.llmie_moe_tile_rows(K), self.lib.llmie_moe_tile_rows(F))
         # more than two rows per expert on average: the tensor cores, which fetch an expert's matrices once for up to 128 rows (the
-        # CUDA-core product fetches them once per tile of at most 8; with one or two rows per expert both wait on the same bytes, and
+        # CUDA-core product fetches them once per tile of at most 4; with one or two rows per expert both wait on the same bytes, and
         # the CUDA-core product spreads them over more blocks). The choice looks at sizes only, never at a count on the device
         tc = self.use_tc_experts and h.dtype == torch.bfloat16 and K % 8 == 0 and F % 8 == 0 and pairs > 2 * E
         if not tc and rows < 1:

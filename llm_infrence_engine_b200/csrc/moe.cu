@@ -13,7 +13,7 @@
 namespace {
 
 constexpr int ROUTE_MAX_PER_LANE = 16;   // up to 512 router outputs
-constexpr int MOE_TM = 8;                // most rows of a tile of the grouped product on the CUDA cores
+constexpr int MOE_TM = 4;                // most rows of a tile of the grouped product on the CUDA cores
 constexpr int MOE_COLS = 32;             // outputs per block there
 constexpr int MOE_ROWS_SMEM = 96 * 1024; // what a tile's rows may take of shared memory
 constexpr int SORT_THREADS = 1024;
@@ -142,7 +142,7 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x));
 // The row a of a place is x[row_map[place] / row_div] (the token of the pair that sits there), or x[place] without a map.
 // A sum runs over K in one order whatever the tile holds: a place's result does not depend on its neighbours.
 template <typename T, typename TO, bool GATED>
-__global__ void __launch_bounds__(256) moe_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_map, int row_div, const T* __restrict__ w,
+__global__ void __launch_bounds__(256, 2) moe_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_map, int row_div, const T* __restrict__ w,
                                                        const int* __restrict__ offsets, const int* __restrict__ tiles, TO* __restrict__ out, int F,
                                                        int K, int tile_rows) {
     extern __shared__ __align__(16) float moe_rows_smem[];   // [tile_rows][K]
