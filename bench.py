@@ -1059,12 +1059,12 @@ def mufotar_kernel_points(torch, pk) -> dict:
         w_router, corr = torch.randn(E + ident, W, device=dev).to(bf) * 0.05, torch.zeros(E + ident, device=dev)
         wgu, wdn = torch.randn(E, 2 * eff, W, device=dev).to(bf) * 0.02, torch.randn(E, W, eff, device=dev).to(bf) * 0.02
         y = torch.zeros(N, W, device=dev)
-        ids, wts = K.moe_route(K.linear(h, w_router, out_dtype=torch.float32), corr, top)
+        ids, wts = K.moe_router(h, w_router, corr, top)
         real = int((ids < E).sum())
         used = int(torch.unique(ids[ids < E]).numel())
         fl = 6.0 * real * W * eff
         moved = used * 3 * eff * W * 2 + N * W * (2 + 4)
-        out[f"router_{what}_mufotar"] = entry(_time_graph(lambda: K.moe_route(K.linear(h, w_router, out_dtype=torch.float32), corr, top), torch), N * W * 2 + (E + ident) * W * 2)
+        out[f"router_{what}_mufotar"] = entry(_time_graph(lambda: K.moe_router(h, w_router, corr, top), torch), N * W * 2 + (E + ident) * W * 2)
         out[f"experts_{what}_mufotar"] = entry(_time_graph(lambda: K.moe_experts(h, ids, wts, wgu, wdn, add_to=y), torch), moved, fl)
         wd_gu, wd_dn = torch.randn(2 * top * eff, W, device=dev).to(bf) * 0.02, torch.randn(W, top * eff, device=dev).to(bf) * 0.02
         out[f"dense_unit_{what}_zepalorn"] = entry(_time_graph(lambda: K.linear(K.gate_up_act(h, wd_gu, bf, glu=(7.0, 1.702, 1.0)), wd_dn, add_to=y), torch),

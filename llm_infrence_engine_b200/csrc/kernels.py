@@ -107,7 +107,7 @@ class CudaKernels:
                    "llmie_layernorm", "llmie_group_rmsnorm_gate", "llmie_dual_rmsnorm_mix", "llmie_glu_clamped", "llmie_qk_norm_rope_store",
                    "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan", "llmie_zero_fresh_states",
                    "llmie_selective_scan", "llmie_weighted_pair", "llmie_moe_route", "llmie_moe_sort", "llmie_moe_gemm", "llmie_moe_combine",
-                   "llmie_moe_tile_rows", "llmie_moe_gather", "llmie_moe_grouped_tc", "llmie_moe_grouped_tc_rows"):
+                   "llmie_moe_tile_rows", "llmie_moe_router", "llmie_moe_gather", "llmie_moe_grouped_tc", "llmie_moe_grouped_tc_rows"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = self._gate_up_glu_pair = None
@@ -1354,6 +1354,31 @@ class CudaKernels:
         ids = torch.empty((N, top), dtype=torch.int32, device=logits.device)
         weights = torch.empty((N, top), dtype=torch.float32, device=logits.device)
         self._check(self.lib.llmie_moe_route(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), N, total, top, self._stream()), "moe_route")
+        return ids, weights
+
+    def moe_router(self, h, w_router, correction, top: int):
+        """A router from the rows themselves: ``moe_route`` of the 32-bit logits ``h w_router^T`` (``h`` as it is stored). The few rows of
+        a decode step, and float32 always, take one kernel that makes a token's logits and its choice (the sum over the inputs runs in one
+        order whatever the step holds); prompt portions in bfloat16 take the tensor-core product with 32-bit output and the choice kernel."""
+        self._need(h, "h", None, 2)
+        self._need(w_router, "w_router", h.dtype, 2)
+        N, K = h.shape
+        total = w_router.shape[0]
+        fused = (h.dtype == torch.float32 or N <= self.tc_max_rows) and (K + total + 4) * 4 <= 200 * 1024
+        if not fused:
+            return self.moe_route(self.linear(h, w_router, out_dtype=torch.float32), correction, top)
+        if w_router.shape[1] != K:
+            raise KernelError(f"moe_router: h has {K} columns, the router {w_router.shape[1]}")
+        if correction is not None:
+            self._need(correction, "correction", torch.float32, 1)
+            if correction.shape[0] != total:
+                raise KernelError("moe_router: the correction needs one entry per router output")
+        if not 1 <= top <= total or total > 512:
+            raise KernelError(f"moe_router: {top} of {total} router outputs cannot be chosen (at most 512 outputs)")
+        ids = torch.empty((N, top), dtype=torch.int32, device=h.device)
+        weights = torch.empty((N, top), dtype=torch.float32, device=h.device)
+        self._check(self.lib.llmie_moe_router(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(ids), _ptr(weights), N, K, total, top, self._dt(h, "h"),
+                                              self._stream()), "moe_router")
         return ids, weights
 
     def moe_experts(self, h, ids, weights, w_gate_up, w_down, add_to):

@@ -21,19 +21,15 @@ constexpr int SORT_MAX_EXPERTS = 4096;
 
 // One warp per token: s = softmax(logits) over all `total` router outputs; the `top` outputs with the largest s + correction are
 // chosen (of equal scores the lower index first); their weights are s / (sum of the chosen s + 1e-20).
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
-                                                        int* __restrict__ ids, float* __restrict__ weights, int N, int total, int top) {
-    pdl_trigger();
-    pdl_wait();
-    const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (n >= N) return;
+// (one warp: token n's row of logits, in global or shared memory)
+__device__ __forceinline__ void route_token(const float* __restrict__ row, const float* __restrict__ correction, int* __restrict__ ids,
+                                            float* __restrict__ weights, int n, int total, int top, int lane) {
     float s[ROUTE_MAX_PER_LANE], c[ROUTE_MAX_PER_LANE];
     float mx = -INFINITY;
 #pragma unroll
     for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
         const int e = lane + 32 * j;
-        s[j] = e < total ? logits[(size_t)n * total + e] : -INFINITY;
+        s[j] = e < total ? row[e] : -INFINITY;
         mx = fmaxf(mx, s[j]);
     }
     mx = warp_max(mx);
@@ -84,6 +80,63 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     __syncwarp();
     const float inv = 1.0f / (chosen_sum + 1e-20f);
     for (int k = lane; k < top; k += 32) weights[(size_t)n * top + k] *= inv;
+}
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                                                        int* __restrict__ ids, float* __restrict__ weights, int N, int total, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (n >= N) return;
+    route_token(logits + (size_t)n * total, correction, ids, weights, n, total, top, threadIdx.x & 31);
+}
+
+// The router's product and its choice in one kernel, a block per token: the token's row lies in shared memory as floats, the warps
+// share the router's outputs (a warp's lanes walk an output's weight row in 16-byte pieces; the sum runs over K in one order whatever
+// the step holds), and the first warp chooses from the logits in shared memory. For the few rows of a decode step, where the product
+// alone would be a kernel that walks K in one block.
+constexpr int ROUTER_THREADS = 256;
+template <typename T>
+__global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ correction,
+                                                                    int* __restrict__ ids, float* __restrict__ weights, int K, int total, int top) {
+    extern __shared__ __align__(16) float router_smem[];   // [K] the row, then [total] the logits
+    constexpr int VN = Vec16<T>::N;
+    float* row = router_smem;
+    float* logits = router_smem + ((K + 3) & ~3);
+    pdl_trigger();
+    const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool vec = (K % VN) == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)w & 15) == 0;
+    pdl_wait();
+    const T* src = h + (size_t)n * K;
+    if (vec) {
+        for (int k = threadIdx.x * VN; k < K; k += ROUTER_THREADS * VN) {
+            float v[VN];
+            Vec16<T>::load(src + k, v);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) row[k + i] = v[i];
+        }
+    } else {
+        for (int k = threadIdx.x; k < K; k += ROUTER_THREADS) row[k] = to_f32(src[k]);
+    }
+    __syncthreads();
+    for (int e = warp; e < total; e += ROUTER_THREADS / 32) {
+        const T* we = w + (size_t)e * K;
+        float acc = 0.f;
+        if (vec) {
+            for (int k = lane * VN; k < K; k += 32 * VN) {
+                float v[VN];
+                Vec16<T>::load(we + k, v);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) acc = fmaf(row[k + i], v[i], acc);
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) acc = fmaf(row[k], to_f32(we[k]), acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) logits[e] = acc;
+    }
+    __syncthreads();
+    if (warp == 0) route_token(logits, correction, ids, weights, n, total, top, lane);
 }
 
 // One block: the step's (token, choice) pairs counted per expert, the experts' runs laid out one behind the other, every pair
@@ -301,6 +354,33 @@ LLMIE_API int llmie_moe_route(const float* logits, const float* correction, int*
     if (N <= 0) return 0;
     if (total <= 0 || total > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > total) return LLMIE_ERR_BAD_ARGUMENT;
     return launch_kernel(moe_route_kernel, dim3((N + 3) / 4), dim3(128), 0, s, logits, correction, ids, weights, N, total, top);
+}
+
+// ids, weights [N, top] from the rows h [N, K] and the router's matrix w [total, K] of the same type (float or bfloat16): the product in
+// 32-bit and the choice, one launch. The row and the logits must fit the shared memory (K + total floats: up to about 50,000).
+LLMIE_API int llmie_moe_router(const void* h, const void* w, const float* correction, int* ids, float* weights, int N, int K, int total, int top,
+                               int dtype, cudaStream_t s) {
+    if (N <= 0) return 0;
+    if (K <= 0 || total <= 0 || total > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > total) return LLMIE_ERR_BAD_ARGUMENT;
+    const size_t smem = ((size_t)((K + 3) & ~3) + total) * sizeof(float);
+    if (smem > 200 * 1024) return LLMIE_ERR_BAD_ARGUMENT;
+    static size_t allowed_f = 48 * 1024, allowed_b = 48 * 1024;
+    if (dtype == DT_F32) {
+        if (smem > allowed_f) {
+            cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            allowed_f = 200 * 1024;
+        }
+        return launch_kernel(moe_router_kernel<float>, dim3(N), dim3(ROUTER_THREADS), smem, s, (const float*)h, (const float*)w, correction, ids, weights, K,
+                             total, top);
+    }
+    if (smem > allowed_b) {
+        cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        allowed_b = 200 * 1024;
+    }
+    return launch_kernel(moe_router_kernel<bf16>, dim3(N), dim3(ROUTER_THREADS), smem, s, (const bf16*)h, (const bf16*)w, correction, ids, weights, K, total,
+                         top);
 }
 
 // Rows per tile of the grouped product on the CUDA cores for rows of K numbers: as many as fit the shared memory, at most MOE_TM;

@@ -157,8 +157,7 @@ class RoutedExperts(FeedForward):
 
     def forward(self, ctx, h, residual):
         K = ctx.K
-        logits = K.linear(h, self.w_router, out_dtype=torch.float32)
-        ids, weights = K.moe_route(logits, self.correction, self.top)
+        ids, weights = K.moe_router(h, self.w_router, self.correction, self.top)
         K.moe_experts(h, ids, weights, self.w_gate_up, self.w_down, add_to=residual)
         if self.shared is not None:
             self.shared.forward(ctx, h, residual)

@@ -187,6 +187,30 @@ def test_router_takes_the_largest_corrected_scores_and_weighs_by_the_plain_ones(
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,Kd,total,top", [(1, 64, 5, 2), (9, 44, 3, 3), (130, 72, 7, 1), (33, 1000, 70, 6), (300, 264, 12, 4), (5, 14000, 9, 2)])
+def test_router_from_the_rows(K, dtype, N, Kd, total, top):
+    """The product and the choice in one kernel (few rows, float32) or as product + choice (prompt portions in bfloat16): the same
+    experts as the torch statement wherever its scores are not nearly equal, and the weights of those."""
+    ref, T = TorchKernels(), TD[dtype]
+    h, w = rnd(N, Kd, seed=1).to(T), (rnd(total, Kd, seed=2) / Kd ** 0.5 * 3).to(T)
+    corr = rnd(total, seed=3) * 0.05
+    ids, wt = K.moe_router(h.cuda(), w.cuda(), corr.cuda(), top)
+    ids2, wt2 = ref.moe_router(h, w, corr, top)
+    s = torch.softmax(h.double() @ w.double().T, -1) + corr.double()
+    order = torch.sort(s, -1, descending=True).values
+    sure = torch.ones(N, dtype=torch.bool) if top == total else (order[:, top - 1] - order[:, top]) > 1e-3
+    if top > 1:
+        sure &= (order[:, :top - 1] - order[:, 1:top]).min(-1).values > 1e-3   # (the order among the chosen)
+    assert bool(sure.any())
+    assert torch.equal(ids.cpu()[sure], ids2[sure])
+    assert float((wt.cpu()[sure] - wt2[sure]).abs().max()) < (1e-5 if dtype == "float32" else 2e-3)
+    one = K.moe_router(h[N - 1:].cuda(), w.cuda(), corr.cuda(), top)
+    if dtype == "float32":
+        assert torch.equal(one[0], ids[N - 1:]) and torch.equal(one[1], wt[N - 1:]), "a token's choice does not depend on the batch"
+    K.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("N,E,ident,top,Kd,F", [(7, 8, 2, 2, 256, 96), (70, 3, 0, 2, 40, 24), (200, 5, 3, 4, 64, 36), (1, 4, 1, 1, 16, 8), (700, 6, 1, 3, 128, 72),
                                                 (300, 2, 4, 5, 48, 16), (1500, 16, 0, 2, 264, 200), (400, 3, 1, 2, 40, 20), (130, 2, 0, 2, 72, 136)])
 def test_routed_experts(K, dtype, N, E, ident, top, Kd, F):

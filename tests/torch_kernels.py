@@ -374,6 +374,9 @@ class TorchKernels:
         w = torch.gather(s, 1, ids)
         return ids.to(torch.int32), w / (w.sum(-1, keepdim=True) + 1e-20)
 
+    def moe_router(self, h, w_router, correction, top):
+        return self.moe_route(h.float() @ w_router.float().T, correction, top)
+
     def moe_experts(self, h, ids, weights, w_gate_up, w_down, add_to):
         E, F = w_gate_up.shape[0], w_gate_up.shape[1] // 2
         x = h.float()
