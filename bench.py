@@ -1076,7 +1076,7 @@ def mufotar_kernel_points(torch, pk) -> dict:
     out["layernorm_bias_mufotar"] = entry(_time_graph(lambda: K.layernorm(res, w, 1e-6, bf, bias=bb), torch), N * W * (4 + 2))
     out["layernorm_zepalorn"] = entry(_time_graph(lambda: K.layernorm(res, w, 1e-6, bf), torch), N * W * (4 + 2))
     a2, b2, y = torch.randn(N, W, device=dev), torch.randn(N, W, device=dev), torch.zeros(N, W, device=dev)
-    out["weighted_pair_mufotar"] = entry(_time_graph(lambda: K.weighted_pair(a2, b2, 1.2, 0.9, y), torch), N * W * (4 + 4 + 4 + 4))
+    out["weighted_pair_mufotar"] = entry(_time_graph(lambda: K.weighted_pair(a2, b2, 1.3, 0.7, y), torch), N * W * (4 + 4 + 4 + 4))
     out["mean_of_two_zepalorn"] = entry(_time_graph(lambda: K.dual_rmsnorm_mix(a2, b2, w, w, 1e-6, 0.5, y), torch), N * W * (4 + 4 + 4 + 4))
     o, g, nw = torch.randn(N, dh * dv, device=dev), torch.randn(N, dh * dv, device=dev).to(bf), torch.ones(dv, device=dev)
     out["gated_norm_silu_mufotar"] = entry(_time_graph(lambda: K.group_rmsnorm_gate(o, g, 0, nw, dv, 1e-6, False, bf, gate_act="silu"), torch), N * dh * dv * (4 + 2 + 2))

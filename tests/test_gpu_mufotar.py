@@ -154,12 +154,12 @@ def test_layernorm_with_bias_gated_norm_pair_cap_and_gelu_unit(K, dtype):
     for ta in (torch.float32, T):
         a, c, y = rnd(9, 40, seed=7).to(ta), rnd(9, 40, seed=8), rnd(9, 40, seed=9)
         yd = y.clone().cuda()
-        ref.weighted_pair(a, c, 1.2, 0.9, y)
-        K.weighted_pair(a.cuda(), c.cuda(), 1.2, 0.9, yd)
+        ref.weighted_pair(a, c, 1.3, 0.7, y)
+        K.weighted_pair(a.cuda(), c.cuda(), 1.3, 0.7, yd)
         close(yd, y, "float32", "weighted pair")
     lg = rnd(5, 77, seed=10, scale=20.0)
-    close(K.softcap(lg.clone().cuda(), 15.0), ref.softcap(lg, 15.0), "float32", "softcap")
-    assert float(K.softcap(lg.clone().cuda(), 15.0).abs().max()) <= 15.0
+    close(K.softcap(lg.clone().cuda(), 11.0), ref.softcap(lg, 11.0), "float32", "softcap")
+    assert float(K.softcap(lg.clone().cuda(), 11.0).abs().max()) <= 11.0
     for M, I, Kd in ((5, 96, 64), (300, 96, 64), (1100, 264, 96)):
         x, w = rnd(M, Kd, seed=11).to(T), rnd(2 * I, Kd, seed=12, scale=0.3).to(T)
         close(K.gate_up_act(x.cuda(), w.cuda(), T, activation="gelu_tanh"), ref.gate_up_act(x, w, T, activation="gelu_tanh"), dtype, f"gelu unit, {M} rows")
