@@ -59,6 +59,7 @@ class CudaKernels:
         self.use_cluster_gate_up = False  # ... by pairs of blocks that share their weight rows (TMA multicast within a cluster of two)
         self.use_pair_gate_up = True     # ... by pairs of multiprocessors on tiles of 256 rows (tcgen05 cta_group::2) ...
         self.pair_gate_up_min_rows = 1024  # ... from this many rows on (measured: 3 to 8 % faster at 2,048 rows, 5 % slower at 512)
+        self.use_fused_router = os.environ.get("LLMIE_FUSED_ROUTER", "1") != "0"   # a router's product and choice in one kernel (few rows, float32)
         self.use_tc_experts = True     # routed experts with many rows per expert: both grouped products on tcgen05 (bfloat16)
         self.use_tc_gate_up = True     # prompt portions: gate/up product with the activation as its epilogue, one tcgen05 kernel
         self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel ...
@@ -1364,7 +1365,7 @@ class CudaKernels:
         self._need(w_router, "w_router", h.dtype, 2)
         N, K = h.shape
         total = w_router.shape[0]
-        fused = (h.dtype == torch.float32 or N <= self.tc_max_rows) and (K + total + 4) * 4 <= 200 * 1024
+        fused = self.use_fused_router and (h.dtype == torch.float32 or N <= self.tc_max_rows) and (K + total + 4) * 4 <= 200 * 1024
         if not fused:
             return self.moe_route(self.linear(h, w_router, out_dtype=torch.float32), correction, top)
         if w_router.shape[1] != K:
