@@ -1407,7 +1407,8 @@ class CudaKernels:
         # more than two rows per expert on average: the tensor cores, which fetch an expert's matrices once for up to 128 rows (the
         # CUDA-core product fetches them once per tile of at most 4; with one or two rows per expert both wait on the same bytes, and
         # the CUDA-core product spreads them over more blocks). The choice looks at sizes only, never at a count on the device
-        tc = self.use_tc_experts and h.dtype == torch.bfloat16 and K % 8 == 0 and F % 8 == 0 and pairs > 2 * E
+        tc = (self.use_tc_experts and h.dtype == torch.bfloat16 and K % 8 == 0 and F % 8 == 0 and pairs > 2 * E
+              and w_gate_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0 and h.data_ptr() % 16 == 0)
         if not tc and rows < 1:
             raise KernelError(f"moe_experts: rows of {max(K, F)} numbers do not fit the shared memory of the product for few rows")
         tile_rows = self.lib.llmie_moe_grouped_tc_rows() if tc else rows
