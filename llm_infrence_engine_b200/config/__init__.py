@@ -1,4 +1,4 @@
 from .engine_config import EngineConfig
-from .model_config import ConfigError, LuvutarConfig, Qwen2Config, architecture_name, read_config_json
+from .model_config import ConfigError, LuvutarConfig, MemilornConfig, Qwen2Config, architecture_name, read_config_json
 
-__all__ = ["ConfigError", "EngineConfig", "LuvutarConfig", "Qwen2Config", "architecture_name", "read_config_json"]
+__all__ = ["ConfigError", "EngineConfig", "LuvutarConfig", "MemilornConfig", "Qwen2Config", "architecture_name", "read_config_json"]

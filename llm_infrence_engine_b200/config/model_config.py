@@ -689,3 +689,180 @@ class MufotarConfig:
             o = self.layers[src]
             if (o.kind, o.mixer, o.mlp) != (layer.kind, layer.mixer, layer.mlp):
                 raise ConfigError(f"layers[{i}] runs on the weights of layer {src}, but the rest of its entry differs from that layer's")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Memilorn: a decoder whose config.json lists its layers one by one; pre-norm layers (layer norms with a weight) whose sublayer
+# results pass a layer scale; a run of layers may loop on the same weights, the embedding added again before every further pass.
+# Mixers: a matrix memory with exponential gates (mLSTM), latent attention without positions, grouped attention whose heads'
+# scores are mixed before the softmax. Feed-forward: routed experts with sigmoid scores on the experts' inputs, and a shared one.
+
+@dataclass(frozen=True)
+class MatrixMemoryConfig:
+    """``mlstm``: ``heads`` heads with query/key size ``dim`` and value size ``vdim``; both gates' pre-activations are bounded by
+    ``gate_cap * tanh(x / gate_cap)`` (None: not bounded)."""
+
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: Optional[float]
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "MatrixMemoryConfig":
+        cap = _number(m, "gate_cap", where) if m.get("gate_cap") is not None else None
+        if cap is not None and not cap > 0:
+            raise ConfigError(f"config.json: {where}'gate_cap' must be positive, got {cap}")
+        dim = _pos_int(m, "dim", where)
+        if dim > 256:
+            raise ConfigError(f"config.json: {where}'dim' {dim} is more than the 256 entries of a memory column that are built")
+        return cls(_pos_int(m, "heads", where), dim, _pos_int(m, "vdim", where) if "vdim" in m else dim, cap)
+
+
+@dataclass(frozen=True)
+class PlainLatentConfig:
+    """``latent_attention`` without positions: queries straight from the input, keys and values rebuilt from a normed latent of
+    ``kv_rank`` entries per token."""
+
+    heads: int
+    dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "PlainLatentConfig":
+        dim = _pos_int(m, "dim", where)
+        return cls(_pos_int(m, "heads", where), dim, _pos_int(m, "vdim", where) if "vdim" in m else dim, _pos_int(m, "kv_rank", where),
+                   _number(m, "scale", where))
+
+
+@dataclass(frozen=True)
+class TalkingAttentionConfig:
+    """``attention``: grouped heads, the first ``rot.dims`` entries of a head turned in neighbouring pairs, scores bounded by
+    ``softcap`` and mixed between the heads before the softmax, a sink and a gate per head."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: Optional[RotationConfig]
+    softcap: Optional[float]
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "TalkingAttentionConfig":
+        heads, kv_heads = _pos_int(m, "heads", where), _pos_int(m, "kv_heads", where)
+        if heads % kv_heads:
+            raise ConfigError(f"config.json: {where}{heads} heads cannot share {kv_heads} kv_heads")
+        dim = _pos_int(m, "dim", where)
+        rot = _opt_sub(m, "rot", where)
+        rot = RotationConfig.from_dict(rot, where + "rot.") if rot else None
+        if rot is not None and rot.dims > dim:
+            raise ConfigError(f"config.json: {where}rot.dims {rot.dims} is more than dim {dim}")
+        if rot is not None and rot.factor is not None:
+            raise ConfigError(f"config.json: {where}rot.scaling is not part of this architecture")
+        cap = _number(m, "softcap", where) if m.get("softcap") is not None else None
+        if cap is not None and not cap > 0:
+            raise ConfigError(f"config.json: {where}'softcap' must be positive, got {cap}")
+        return cls(heads, kv_heads, dim, _pos_int(m, "vdim", where) if "vdim" in m else dim, _number(m, "scale", where), rot, cap)
+
+
+@dataclass(frozen=True)
+class SigmoidExpertsConfig:
+    """``mlp.kind = "moe"``: ``experts`` clamped gated units of width ``ff`` (bound ``limit``) of which a token uses ``top``, chosen
+    and weighted by the sigmoid of the router's outputs; ``shared_ff`` / ``shared_limit``: a unit that every token uses (None: none)."""
+
+    experts: int
+    top: int
+    ff: int
+    limit: float
+    shared_ff: Optional[int]
+    shared_limit: float
+
+    @classmethod
+    def from_dict(cls, mlp: Mapping[str, Any], where: str) -> "SigmoidExpertsConfig":
+        r, e = _sub(mlp, "router", where), _sub(mlp, "expert", where)
+        shared = _opt_sub(mlp, "shared", where)
+        c = cls(_pos_int(r, "experts", where + "router."), _pos_int(r, "top", where + "router."), _pos_int(e, "ff", where + "expert."),
+                _number(e, "limit", where + "expert."), _pos_int(shared, "ff", where + "shared.") if shared else None,
+                _number(shared, "limit", where + "shared.") if shared else 0.0)
+        if c.top > c.experts:
+            raise ConfigError(f"config.json: {where}router.top {c.top} is more than the {c.experts} experts")
+        if c.experts > 512:
+            raise ConfigError(f"config.json: {where}router: at most 512 experts are built")
+        if not c.limit > 0 or (shared and not c.shared_limit > 0):
+            raise ConfigError(f"config.json: {where}the limit of a clamped unit must be positive")
+        return c
+
+
+@dataclass(frozen=True)
+class MemilornLayerConfig:
+    kind: str                       # "mlstm", "latent_attention" or "attention"
+    mixer: Any
+    mlp: Optional[SigmoidExpertsConfig]   # None: the layer is a mixer alone
+
+
+@dataclass(frozen=True)
+class MemilornConfig:
+    """The whole of a Memilorn config.json: vocabulary, width, norm epsilon, the list of layers and the loop (layers
+    ``loop_start .. loop_stop - 1`` run ``loop_times`` times in a row on the same weights; no ``loop``: every layer once)."""
+
+    architecture = "Memilorn"
+
+    vocab: int
+    width: int
+    eps: float
+    layers: tuple
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+
+    _MIXERS = {"mlstm": MatrixMemoryConfig, "latent_attention": PlainLatentConfig, "attention": TalkingAttentionConfig}
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "MemilornConfig":
+        if not isinstance(d.get("layers"), (list, tuple)) or not d["layers"]:
+            raise ConfigError("config.json: 'layers' must be a list with at least one layer")
+        layers = []
+        for i, layer in enumerate(d["layers"]):
+            where = f"layers[{i}]."
+            if not isinstance(layer, Mapping):
+                raise ConfigError(f"config.json: layers[{i}] must be an object")
+            kind = layer.get("type")
+            if kind not in cls._MIXERS:
+                raise ConfigError(f"config.json: {where}type {kind!r} is not one of {sorted(cls._MIXERS)}")
+            mixer = cls._MIXERS[kind].from_dict(_sub(layer, "mixer", where), where + "mixer.")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, Mapping) or mlp.get("kind", "moe") != "moe":
+                    raise ConfigError(f"config.json: {where}mlp must be null or an object of kind 'moe'")
+                mlp = SigmoidExpertsConfig.from_dict(mlp, where + "mlp.")
+            layers.append(MemilornLayerConfig(kind, mixer, mlp))
+        loop = _opt_sub(d, "loop", "")
+        start = stop = 0
+        times = 1
+        if loop:
+            for key in ("start", "stop", "times"):
+                v = loop.get(key)
+                if isinstance(v, bool) or not isinstance(v, int) or v < 0:
+                    raise ConfigError(f"config.json: loop.{key} must be a count, got {v!r}")
+            start, stop, times = loop["start"], loop["stop"], loop["times"]
+        cfg = cls(_pos_int(d, "vocab", ""), _pos_int(d, "width", ""), _number(_sub(d, "norm", ""), "eps", "norm."), tuple(layers), start, stop, times)
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if not self.eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.eps}")
+        if not 0 <= self.loop_start <= self.loop_stop <= len(self.layers):
+            raise ConfigError(f"loop: layers {self.loop_start} .. {self.loop_stop} - 1 are not a run of the {len(self.layers)} layers")
+        if self.loop_times < 1:
+            raise ConfigError(f"loop.times must be at least 1, got {self.loop_times}")
+
+    def running_order(self) -> list:
+        """``(layer, pass, first of a further pass)`` in the order the layers run: the layers before the loop, the looped run
+        ``loop_times`` times, the rest."""
+        order = [(i, 0, False) for i in range(self.loop_start)]
+        for t in range(self.loop_times):
+            order += [(i, t, t > 0 and i == self.loop_start) for i in range(self.loop_start, self.loop_stop)]
+        return order + [(i, 0, False) for i in range(self.loop_stop, len(self.layers))]

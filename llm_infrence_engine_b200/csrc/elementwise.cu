@@ -25,6 +25,24 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
+// x[n, :] += table[ids[n], :] * scale: the embedding added into a stream that already holds something
+template <typename T>
+__global__ void embed_add_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int H, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const T* row = table + (size_t)ids[n] * H;
+    float* o = out + (size_t)n * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] += to_f32(row[i]) * scale;
+}
+
+LLMIE_API int llmie_embed_add(const int* ids, const void* table, float* out, int N, int H, int dtype, float scale, cudaStream_t s) {
+    if (N <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == DT_F32) return launch_kernel(embed_add_kernel<float>, dim3(N), dim3(threads), 0, s, ids, (const float*)table, out, H, scale);
+    return launch_kernel(embed_add_kernel<bf16>, dim3(N), dim3(threads), 0, s, ids, (const bf16*)table, out, H, scale);
+}
+
 LLMIE_API int llmie_embed(const int* ids, const void* table, float* out, int N, int H, int dtype, float scale, cudaStream_t s) {
     if (N <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;

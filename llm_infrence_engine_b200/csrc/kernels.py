@@ -82,7 +82,8 @@ class CudaKernels:
         # normalises in one pass: (streams, the sublayer's result, mix, out coefficients)
         self._pending_streams: Optional[tuple] = None
         # A sublayer's result whose layer norm is to be added into the residual stream waits here for the norm of the next
-        # sublayer, which adds and normalises in one pass: (stream, result, the post-norm's weight, eps)
+        # sublayer, which adds and normalises in one pass: (stream, result, the post-norm's weight, eps, plain); ``plain``: the result
+        # is only scaled element by element by the weight (a layer scale), not normed
         self._pending_post: Optional[tuple] = None
         self._state_lists: dict = {}   # the addresses of a runner's state tensors on the device (zero_fresh_states)
         self._fresh: list = []   # zeroed tensors of ``zeros_like_rows`` that nothing has been added into yet
@@ -108,7 +109,9 @@ class CudaKernels:
                    "llmie_layernorm", "llmie_group_rmsnorm_gate", "llmie_dual_rmsnorm_mix", "llmie_glu_clamped", "llmie_qk_norm_rope_store",
                    "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan", "llmie_zero_fresh_states",
                    "llmie_selective_scan", "llmie_weighted_pair", "llmie_moe_route", "llmie_moe_sort", "llmie_moe_gemm", "llmie_moe_combine",
-                   "llmie_moe_tile_rows", "llmie_moe_router", "llmie_moe_gather", "llmie_moe_grouped_tc", "llmie_moe_grouped_tc_rows"):
+                   "llmie_moe_tile_rows", "llmie_moe_router", "llmie_moe_gather", "llmie_moe_grouped_tc", "llmie_moe_grouped_tc_rows",
+                   "llmie_embed_add", "llmie_mlstm_prepare", "llmie_mlstm_scan", "llmie_mlstm_finish", "llmie_paged_attention_talk",
+                   "llmie_attention_talk_slice"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = self._gate_up_glu_pair = None
@@ -187,6 +190,19 @@ class CudaKernels:
         self._check(self.lib.llmie_embed(_ptr(token_ids), _ptr(table), _ptr(out), N, H, self._dt(table, "table"), ctypes.c_float(scale),
                                         self._stream()), "embed")
         return out
+
+    def embed_add(self, token_ids, table, residual, scale: float = 1.0):
+        """``residual += table[token] * scale``: the embedding added once more into a stream that already holds something. A sublayer's
+        result that still waits to be added stays waiting (additions commute); only a put-off library product is added first."""
+        self._need(token_ids, "token_ids", torch.int32, 1)
+        self._need(table, "table", None, 2)
+        self._need(residual, "residual", torch.float32, 2)
+        if tuple(residual.shape) != (token_ids.shape[0], table.shape[1]):
+            raise KernelError(f"embed_add: the stream is {list(residual.shape)}, the tokens' rows are [{token_ids.shape[0]}, {table.shape[1]}]")
+        if self._pending_add is not None or self._pending_streams is not None:
+            self.flush()
+        self._check(self.lib.llmie_embed_add(_ptr(token_ids), _ptr(table), _ptr(residual), token_ids.shape[0], table.shape[1], self._dt(table, "table"),
+                                            ctypes.c_float(scale), self._stream()), "embed_add")
 
     def feed_tokens(self, token_ids, source_rows, previous_tokens):
         """``token_ids[i] = previous_tokens[source_rows[i]]`` wherever ``source_rows[i] >= 0`` (all int32, on the device)."""
@@ -277,9 +293,9 @@ class CudaKernels:
             self._check(self.lib.llmie_streams_update(_ptr(xs), _ptr(y), self._dt(y, "y"), int(self._clears(y)), _ptr(mix), _ptr(coef_out), N, S, H,
                                                       self._stream()), "streams_update")
         if self._pending_post is not None:
-            x, y, w_post, eps = self._pending_post
+            x, y, w_post, eps, plain = self._pending_post
             self._pending_post = None
-            self._layernorm(x, y, w_post, None, eps, None, None, "post_norm_add")
+            self._layernorm(x, y, w_post, None, eps, None, None, "post_norm_add", post_plain=plain)
 
     def _take_pending(self, residual, out_dtype):
         """The put-off addend for ``residual`` if there is one that the norm kernel can add on its way (same dtype as its output)."""
@@ -943,13 +959,14 @@ class CudaKernels:
 
     def attention_ext(self, q, q_col, num_heads, num_kv_heads, head_dim, v_head_dim, k_pool, v_pool, block_table, token_seq, positions,
                       page_size, scale, window, max_context, temp=(0.0, 0), rel=None, rel_rows=None, sink=None, gate=None, gate_col=0,
-                      gate_per_head=False, batch=None, num_splits=None, keep_first=0, chunk=0, softcap=0.0):
+                      gate_per_head=False, batch=None, num_splits=None, keep_first=0, chunk=0, softcap=0.0, talk=None):
         """Paged attention with extras: the query heads are columns ``q_col ..`` of ``q``; ``v_pool=None`` reads the values out
         of the key rows (their first ``v_head_dim`` entries); ``temp=(coef, every)`` a query temperature by position;
         ``rel [rows, heads]`` with ``rel_rows`` (distance -> row) a bias by distance; ``sink [heads]`` joins the denominator;
         ``gate`` (columns from ``gate_col`` of a tensor with the tokens' rows) an output gate per head or per element;
         ``keep_first`` keys at the request's start stay visible when the ``window`` has passed them; ``chunk`` > 0 lets a position
-        see only the keys of its own run of ``chunk`` positions; ``softcap`` > 0 bounds the scaled scores by ``cap * tanh(s / cap)``."""
+        see only the keys of its own run of ``chunk`` positions; ``softcap`` > 0 bounds the scaled scores by ``cap * tanh(s / cap)``;
+        ``talk [heads, heads]`` (float32) mixes the heads' capped scores before mask and softmax, ``score'_h = sum_g talk[h, g] score_g``."""
         self._need(q, "q", None, 2)
         dt = self._dt(q, "q")
         N = q.shape[0]
@@ -988,6 +1005,10 @@ class CudaKernels:
                 raise KernelError("attention_ext: the gate columns lie outside the rows")
         out = torch.empty((N, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
         esize = q.element_size()
+        if talk is not None:
+            return self._attention_talk(q, q_col, num_heads, num_kv_heads, head_dim, v_head_dim, k_pool, v_pool, block_table, token_seq, positions,
+                                        page_size, scale, window, max_context, talk, sink, gate, gate_col, gate_mode, keep_first, chunk, softcap,
+                                        temp, rel, out, batch)
         max_rows = 0
         tensor_cores = dt == 1 and self.use_mma_attention_ext and batch is not None and (q_col * esize) % 16 == 0 and q.shape[1] % 8 == 0
         masked = bool(keep_first or chunk or softcap)
@@ -1058,8 +1079,89 @@ class CudaKernels:
             self.launches += 1
         return out
 
+    def _attention_talk(self, q, q_col, num_heads, num_kv_heads, head_dim, v_head_dim, k_pool, v_pool, block_table, token_seq, positions, page_size,
+                        scale, window, max_context, talk, sink, gate, gate_col, gate_mode, keep_first, chunk, softcap, temp, rel, out, batch):
+        """Attention whose heads' scores are mixed before the softmax: one block serves all heads of a token and a slice of its keys. The
+        slices lie at fixed places of a request (as many keys as fit the shared memory with all heads' scores), so a token's result
+        depends on its own position alone."""
+        self._need(talk, "talk", torch.float32, 2)
+        if tuple(talk.shape) != (num_heads, num_heads):
+            raise KernelError(f"attention_ext: talk must be [{num_heads}, {num_heads}]")
+        if rel is not None or temp[1]:
+            raise KernelError("attention_ext: talking heads are not built together with a bias by distance or a query temperature")
+        N = q.shape[0]
+        esize = q.element_size()
+        slice_keys = self.lib.llmie_attention_talk_slice(num_heads, head_dim)
+        if slice_keys < 32:
+            raise KernelError(f"attention_ext: {num_heads} talking heads of {head_dim} entries do not fit the kernel's shared memory")
+        splits = max(1, -(-max_context // slice_keys))
+        scratch = self._scratch(N * num_heads * splits * (v_head_dim + 2), q.device) if splits > 1 else None
+        self._check(self.lib.llmie_paged_attention_talk(
+            ctypes.c_void_p(q.data_ptr() + q_col * esize), q.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+            _ptr(token_seq), _ptr(positions), _ptr(talk), _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads, head_dim, v_head_dim, page_size,
+            ctypes.c_float(scale), int(window), splits, slice_keys, _ptr(sink),
+            ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize), 0 if gate is None else gate.shape[1], gate_mode,
+            int(keep_first), int(chunk), ctypes.c_float(softcap), self._dt(q, "q"), self._stream()), "attention_ext (talking heads)")
+        if splits > 1:
+            self.launches += 1
+        return out
+
+    # ------------------------------------------------------------------ the matrix memory with exponential gates
+    def mlstm(self, z, q_col, k_col, v_col, gates, bias_i, bias_f, cap, num_heads, head_dim, v_head_dim, state, mstate, batch):
+        """The mLSTM recurrence over the rows of each request. ``z`` holds q, k (``heads * head_dim`` columns from ``q_col``, ``k_col``) and v
+        (``heads * v_head_dim`` from ``v_col``); ``gates [N, >= 2 heads]`` float32 are the pre-activations ``[W_i h | W_f h]`` of the two
+        gates. With ``i = cap tanh((x_i + b_i) / cap)`` and ``f = ln sigmoid(cap tanh((x_f + b_f) / cap))`` (``cap`` None: no cap), per head:
+        ``m <- max(f + m, i)``; ``S <- exp(f + m_old - m) S + exp(i - m) k v^T``, ``n`` likewise with ``k`` alone. From ``state [slots, heads,
+        v_head_dim + 1, head_dim]`` (the memory column by column, the normaliser as its last column) and ``mstate [slots, heads]``, which
+        are moved on. Returns the numerators ``[N, heads, v_head_dim + 1]`` (``S^T q`` with ``q`` times ``head_dim^-1/2``, then ``n . q``)
+        and ``m [N, heads]``, float32: ``mlstm_finish`` divides, norms and gates."""
+        self._need(z, "z", None, 2)
+        self._need(gates, "gates", torch.float32, 2)
+        self._need(state, "state", torch.float32, 4)
+        self._need(mstate, "mstate", torch.float32, 2)
+        self._need(bias_i, "bias_i", torch.float32, 1)
+        self._need(bias_f, "bias_f", torch.float32, 1)
+        N, H, D, DV = z.shape[0], num_heads, head_dim, v_head_dim
+        if max(q_col, k_col) + H * D > z.shape[1] or v_col + H * DV > z.shape[1] or gates.shape[0] != N or gates.shape[1] < 2 * H:
+            raise KernelError("mlstm: the columns of q, k, v or the gates lie outside the rows")
+        if tuple(state.shape[1:]) != (H, DV + 1, D) or tuple(mstate.shape[1:]) != (H,) or mstate.shape[0] != state.shape[0]:
+            raise KernelError(f"mlstm: state is {list(state.shape)} / {list(mstate.shape)}, expected [slots, {H}, {DV + 1}, {D}] / [slots, {H}]")
+        if bias_i.shape[0] != H or bias_f.shape[0] != H:
+            raise KernelError("mlstm: one bias per head and gate is needed")
+        if D > 256:
+            raise KernelError(f"mlstm: head_dim {D} is more than the 256 entries of a column that the kernel keeps in registers")
+        dev = z.device
+        work = torch.empty((2 * N * H * D + 2 * N * H,), dtype=torch.float32, device=dev)
+        qf, kf = work[:N * H * D], work[N * H * D:2 * N * H * D]
+        ig, fg = work[2 * N * H * D:2 * N * H * D + N * H], work[2 * N * H * D + N * H:]
+        dt = self._dt(z, "z")
+        self._check(self.lib.llmie_mlstm_prepare(_ptr(z), z.shape[1], q_col, k_col, _ptr(gates), gates.shape[1], _ptr(bias_i), _ptr(bias_f),
+                                                 ctypes.c_float(cap or 0.0), ctypes.c_float(D ** -0.5), _ptr(qf), _ptr(kf), _ptr(ig), _ptr(fg), N, H, D, dt,
+                                                 self._stream()), "mlstm (prepare)")
+        num = torch.empty((N, H, DV + 1), dtype=torch.float32, device=dev)
+        m = torch.empty((N, H), dtype=torch.float32, device=dev)
+        self._check(self.lib.llmie_mlstm_scan(_ptr(z), z.shape[1], v_col, _ptr(qf), _ptr(kf), _ptr(ig), _ptr(fg), _ptr(state), _ptr(mstate),
+                                              _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots), _ptr(num), _ptr(m), H, D, DV, batch.num_seqs, dt,
+                                              self._stream()), "mlstm (scan)")
+        return num, m
+
+    def mlstm_finish(self, num, m, gate, gate_col, weight, eps, out_dtype):
+        """``o = num[..., :DV] / (max(|num[..., DV]|, exp(-m)) + 1e-6)``; every head's ``o`` divided by its root mean square, times
+        ``weight [heads * DV]``, times ``sigmoid`` of the gate columns (``heads * DV`` from ``gate_col`` of ``gate``); ``[N, heads * DV]``."""
+        self._need(num, "num", torch.float32, 3)
+        self._need(m, "m", torch.float32, 2)
+        self._need(gate, "gate", out_dtype, 2)
+        self._need(weight, "weight", torch.float32, 1)
+        N, H, DV = num.shape[0], num.shape[1], num.shape[2] - 1
+        if tuple(m.shape) != (N, H) or weight.shape[0] != H * DV or gate.shape[0] != N or gate_col + H * DV > gate.shape[1]:
+            raise KernelError("mlstm_finish: the maxima, the weight or the gate columns do not fit the numerators")
+        out = torch.empty((N, H * DV), dtype=out_dtype, device=num.device)
+        self._check(self.lib.llmie_mlstm_finish(_ptr(num), _ptr(m), ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1],
+                                                _ptr(weight), _ptr(out), N, H, DV, ctypes.c_float(eps), _DT[out_dtype], self._stream()), "mlstm_finish")
+        return out
+
     # ------------------------------------------------------------------ layer norm before and after a sublayer
-    def _layernorm(self, x, y, w_post, w_pre, eps, rows, out_dtype, what, b_pre=None):
+    def _layernorm(self, x, y, w_post, w_pre, eps, rows, out_dtype, what, b_pre=None, post_plain=False):
         self._need(x, "residual", torch.float32, 2)
         N, H = x.shape
         clear = False
@@ -1097,7 +1199,7 @@ class CudaKernels:
         elif y is None:
             return None
         self._check(self.lib.llmie_layernorm(_ptr(x), _ptr(y), y_dt, _ptr(w_post), int(clear), _ptr(w_pre), _ptr(b_pre if w_pre is not None else None), _ptr(out), out_dt, _ptr(rows), n_out, H,
-                                             ctypes.c_float(eps), self._stream()), what)
+                                             ctypes.c_float(eps), int(bool(post_plain)), self._stream()), what)
         if clear and rows is not None:
             y.zero_()   # only the chosen rows were read and cleared; the buffer must be zero for its next user
             self.launches += 1
@@ -1107,23 +1209,33 @@ class CudaKernels:
         """``(x - mean) / sqrt(var + eps) * weight (+ bias)`` of the stream's rows (or of ``rows``), in ``out_dtype``. A sublayer's result
         whose own layer norm still waits to be added into this stream (``post_norm_add``) is added by the same kernel."""
         y = w_post = None
-        if (self._pending_post is not None and self._pending_post[0] is residual and self._pending_post[3] == eps
+        plain = False
+        if (self._pending_post is not None and self._pending_post[0] is residual and (self._pending_post[3] == eps or self._pending_post[4])
                 and self._pending_add is None and self._pending_streams is None):
-            _, y, w_post, _ = self._pending_post
+            _, y, w_post, _, plain = self._pending_post
             if y.dtype == torch.bfloat16 and out_dtype == torch.float32:   # no kernel for this pair: the addition on its own, then the norm
                 y = w_post = None
+                plain = False
                 self.flush()
             else:
                 self._pending_post = None
         else:
             self.flush()
-        return self._layernorm(residual, y, w_post, weight, eps, rows, out_dtype, "layernorm", b_pre=bias)
+        return self._layernorm(residual, y, w_post, weight, eps, rows, out_dtype, "layernorm", b_pre=bias, post_plain=plain)
 
     def post_norm_add(self, residual, y, weight, eps):
         """``residual += layernorm(y) * weight``: put off until the next ``layernorm`` of the same stream (one pass does both)
         or until ``flush``. ``y`` is a zeroed tensor of ``zeros_like_rows`` that the sublayer added its result into."""
         y = self.take_result(y)
-        self._pending_post = (residual, y, weight, float(eps))
+        self._pending_post = (residual, y, weight, float(eps), False)
+
+    def scaled_add(self, residual, y, weight):
+        """``residual += y * weight`` element by element (a layer scale on a sublayer's result): put off until the next ``layernorm``
+        of the same stream (one pass does both) or until ``flush``. ``y`` is a zeroed tensor of ``zeros_like_rows`` that the sublayer
+        added its result into."""
+        y = self.take_result(y)
+        self._need(weight, "weight", torch.float32, 1)
+        self._pending_post = (residual, y, weight, 0.0, True)
 
     def group_rmsnorm_gate(self, x, gate, gate_col, weight, group_size, eps, gate_first, out_dtype, gate_act="sigmoid"):
         """Float32 rows ``x [N, C]`` normed by their root mean square in groups of ``group_size`` channels, with a gate read
@@ -1341,10 +1453,15 @@ class CudaKernels:
         return out
 
     # ------------------------------------------------------------------ routed experts
-    def moe_route(self, logits, correction, top: int):
+    _SCORING = {"softmax": 0, "sigmoid": 1}
+
+    def moe_route(self, logits, correction, top: int, scoring: str = "softmax"):
         """From float32 router logits ``[N, outputs]``: ``s = softmax(logits)``; the ``top`` outputs with the largest ``s + correction``
-        (``correction`` may be None); returns ``(ids [N, top] int32, weights [N, top] float32)`` with the weights ``s / (sum of the chosen s + 1e-20)``."""
+        (``correction`` may be None); returns ``(ids [N, top] int32, weights [N, top] float32)`` with the weights ``s / (sum of the chosen s + 1e-20)``.
+        ``scoring="sigmoid"``: ``s = sigmoid(logits)`` and the weights are the chosen ``s`` as they are."""
         self._need(logits, "logits", torch.float32, 2)
+        if scoring not in self._SCORING:
+            raise KernelError(f"moe_route: scoring '{scoring}' is not built")
         N, total = logits.shape
         if correction is not None:
             self._need(correction, "correction", torch.float32, 1)
@@ -1354,20 +1471,22 @@ class CudaKernels:
             raise KernelError(f"moe_route: {top} of {total} router outputs cannot be chosen (at most 512 outputs)")
         ids = torch.empty((N, top), dtype=torch.int32, device=logits.device)
         weights = torch.empty((N, top), dtype=torch.float32, device=logits.device)
-        self._check(self.lib.llmie_moe_route(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), N, total, top, self._stream()), "moe_route")
+        self._check(self.lib.llmie_moe_route(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), N, total, top, self._SCORING[scoring], self._stream()), "moe_route")
         return ids, weights
 
-    def moe_router(self, h, w_router, correction, top: int):
+    def moe_router(self, h, w_router, correction, top: int, scoring: str = "softmax"):
         """A router from the rows themselves: ``moe_route`` of the 32-bit logits ``h w_router^T`` (``h`` as it is stored). The few rows of
         a decode step, and float32 always, take one kernel that makes a token's logits and its choice (the sum over the inputs runs in one
         order whatever the step holds); prompt portions in bfloat16 take the tensor-core product with 32-bit output and the choice kernel."""
         self._need(h, "h", None, 2)
         self._need(w_router, "w_router", h.dtype, 2)
+        if scoring not in self._SCORING:
+            raise KernelError(f"moe_router: scoring '{scoring}' is not built")
         N, K = h.shape
         total = w_router.shape[0]
         fused = self.use_fused_router and (h.dtype == torch.float32 or N <= self.tc_max_rows) and (K + total + 4) * 4 <= 200 * 1024
         if not fused:
-            return self.moe_route(self.linear(h, w_router, out_dtype=torch.float32), correction, top)
+            return self.moe_route(self.linear(h, w_router, out_dtype=torch.float32), correction, top, scoring)
         if w_router.shape[1] != K:
             raise KernelError(f"moe_router: h has {K} columns, the router {w_router.shape[1]}")
         if correction is not None:
@@ -1378,16 +1497,23 @@ class CudaKernels:
             raise KernelError(f"moe_router: {top} of {total} router outputs cannot be chosen (at most 512 outputs)")
         ids = torch.empty((N, top), dtype=torch.int32, device=h.device)
         weights = torch.empty((N, top), dtype=torch.float32, device=h.device)
-        self._check(self.lib.llmie_moe_router(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(ids), _ptr(weights), N, K, total, top, self._dt(h, "h"),
-                                              self._stream()), "moe_router")
+        self._check(self.lib.llmie_moe_router(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(ids), _ptr(weights), N, K, total, top, self._SCORING[scoring],
+                                              self._dt(h, "h"), self._stream()), "moe_router")
         return ids, weights
 
-    def moe_experts(self, h, ids, weights, w_gate_up, w_down, add_to):
+    def moe_experts(self, h, ids, weights, w_gate_up, w_down, add_to, glu=None, weight_inputs=False):
         """``add_to[t] += sum_k weights[t, k] * expert_(ids[t, k])(h[t])``: expert ``e < E`` is ``down_e(silu(gate_e x) * (up_e x))`` with
         ``w_gate_up [E, 2 F, K]`` (an expert's gate rows, then its up rows) and ``w_down [E, K, F]``; an id from ``E`` on is an identity
         expert whose output is ``h[t]`` itself. The (token, choice) pairs are sorted by expert on the device and every expert's rows go
-        through its matrices as tiles of one grouped product."""
+        through its matrices as tiles of one grouped product. ``glu = (limit, alpha, shift)``: the experts are clamped units,
+        ``down_e(g sigmoid(alpha g) (u + shift))`` with ``g = min(gate_e x, limit)``, ``u = clamp(up_e x, -limit, limit)``. ``weight_inputs``: the
+        weight multiplies the expert's INPUT, ``add_to[t] += sum_k expert(weights[t, k] * h[t])`` (an identity expert then returns the weighted row)."""
         self.flush()
+        limit, alpha, shift = (float(v) for v in glu) if glu is not None else (0.0, 1.0, 0.0)
+        if glu is not None and not limit > 0:
+            raise KernelError("moe_experts: the clamped unit needs a positive limit")
+        fl = (ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift))
+        in_w = _ptr(weights if weight_inputs else None)
         self._need(h, "h", None, 2)
         self._need(add_to, "add_to", torch.float32, 2)
         self._need(ids, "ids", torch.int32, 2)
@@ -1422,18 +1548,19 @@ class CudaKernels:
         if tc:
             xs = torch.empty((pairs, K), dtype=h.dtype, device=dev)
             err = _ptr(self._errors(dev))
-            self._check(self.lib.llmie_moe_gather(_ptr(h), _ptr(perm), _ptr(offsets), E, top, _ptr(xs), pairs, K, self._stream()), "moe_experts (gather)")
+            self._check(self.lib.llmie_moe_gather(_ptr(h), _ptr(perm), _ptr(offsets), E, top, _ptr(xs), pairs, K, in_w, self._stream()), "moe_experts (gather)")
             self._check(self.lib.llmie_moe_grouped_tc(_ptr(xs), pairs, _ptr(w_gate_up), E, _ptr(offsets), _ptr(tiles), max_tiles, _ptr(act), F, K, 1,
-                                                      self.num_sms, err, self._stream()), "moe_experts (gate and up, tcgen05)")
+                                                      self.num_sms, err, *fl, self._stream()), "moe_experts (gate and up, tcgen05)")
             self._check(self.lib.llmie_moe_grouped_tc(_ptr(act), pairs, _ptr(w_down), E, _ptr(offsets), _ptr(tiles), max_tiles, _ptr(y), K, F, 0,
-                                                      self.num_sms, err, self._stream()), "moe_experts (down, tcgen05)")
+                                                      self.num_sms, err, *fl, self._stream()), "moe_experts (down, tcgen05)")
         else:
             self._check(self.lib.llmie_moe_gemm(_ptr(h), _ptr(perm), top, _ptr(w_gate_up), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(act), F, K, 1,
-                                                tile_rows, dt, self._stream()), "moe_experts (gate and up)")
+                                                tile_rows, in_w, *fl, dt, self._stream()), "moe_experts (gate and up)")
             self._check(self.lib.llmie_moe_gemm(_ptr(act), _ptr(None), 1, _ptr(w_down), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(y), K, F, 0,
-                                                tile_rows, dt, self._stream()), "moe_experts (down)")
-        self._check(self.lib.llmie_moe_combine(_ptr(add_to), _ptr(y), _ptr(h), _ptr(place_of), _ptr(weights), N, top, K, dt, self._stream()),
-                    "moe_experts (sum)")
+                                                tile_rows, _ptr(None), *fl, dt, self._stream()), "moe_experts (down)")
+        # (with ``weight_inputs`` the sum is unweighted; the part refuses identity experts in that arrangement, whose rows would need the weight here)
+        self._check(self.lib.llmie_moe_combine(_ptr(add_to), _ptr(y), _ptr(h), _ptr(place_of), _ptr(None if weight_inputs else weights), N, top, K, dt,
+                                               self._stream()), "moe_experts (sum)")
         self._unfresh(add_to)
 
     # ------------------------------------------------------------------ latent attention
@@ -1444,9 +1571,10 @@ class CudaKernels:
         N = z.shape[0]
         if z.shape[1] < q_rank + kv_rank + rot_dim:
             raise KernelError("latent_prepare: the rows are too short for the three parts")
-        self._need(q_norm, "q_norm", torch.float32, 1)
+        if q_rank:
+            self._need(q_norm, "q_norm", torch.float32, 1)
         self._need(kv_norm, "kv_norm", torch.float32, 1)
-        if q_norm.shape[0] != q_rank or kv_norm.shape[0] != kv_rank:
+        if (q_rank and q_norm.shape[0] != q_rank) or kv_norm.shape[0] != kv_rank:
             raise KernelError("latent_prepare: the norm weights do not match the ranks")
         if rot_dims:
             self._need(cos, "cos", torch.float32, 2)
@@ -1458,8 +1586,8 @@ class CudaKernels:
             self._need(kc_pool, "kc_pool", z.dtype, 4)
             if tuple(kc_pool.shape[1:]) != (1, page_size, kv_rank + rot_dim):
                 raise KernelError(f"latent_prepare: the pool is {list(kc_pool.shape)}, expected [pages, 1, {page_size}, {kv_rank + rot_dim}]")
-        cq = torch.empty((N, q_rank), dtype=z.dtype, device=z.device)
-        self._check(self.lib.llmie_latent_prepare(_ptr(z), z.shape[1], q_rank, kv_rank, rot_dim, rot_dims, _ptr(q_norm), _ptr(kv_norm),
+        cq = torch.empty((N, q_rank), dtype=z.dtype, device=z.device) if q_rank else None   # (q_rank 0: no query latent, the cache write alone)
+        self._check(self.lib.llmie_latent_prepare(_ptr(z), z.shape[1], q_rank, kv_rank, rot_dim, rot_dims, _ptr(q_norm if q_rank else None), _ptr(kv_norm),
                                                   ctypes.c_float(eps), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(kc_pool), page_size,
                                                   int(bool(write)), _ptr(cq), N, self._dt(z, "z"), self._stream()), "latent_prepare")
         return cq
@@ -1488,22 +1616,30 @@ class CudaKernels:
 
     def latent_expand(self, o_lat, w_uv, gate, gate_col, num_heads, kv_rank, v_head_dim):
         """``o_lat [N, heads * kv_rank]`` -> ``[N, heads * v_head_dim]``: every head's row times its ``[kv_rank, v_head_dim]`` block of
-        ``w_uv``, times ``sigmoid`` of the gate columns (from ``gate_col`` of ``gate``, one per output element)."""
+        ``w_uv``, times ``sigmoid`` of the gate columns (from ``gate_col`` of ``gate``, one per output element; ``gate=None``: no gate)."""
         self._need(o_lat, "o_lat", None, 2)
         self._need(w_uv, "w_uv", o_lat.dtype)
-        self._need(gate, "gate", o_lat.dtype, 2)
         N = o_lat.shape[0]
         if o_lat.shape[1] != num_heads * kv_rank or w_uv.numel() != num_heads * kv_rank * v_head_dim:
             raise KernelError("latent_expand: o_lat or w_uv does not match the head sizes")
-        if gate.shape[0] != N or gate_col + num_heads * v_head_dim > gate.shape[1]:
-            raise KernelError("latent_expand: the gate columns lie outside the rows")
+        if gate is not None:
+            self._need(gate, "gate", o_lat.dtype, 2)
+            if gate.shape[0] != N or gate_col + num_heads * v_head_dim > gate.shape[1]:
+                raise KernelError("latent_expand: the gate columns lie outside the rows")
         out = torch.empty((N, num_heads * v_head_dim), dtype=o_lat.dtype, device=o_lat.device)
-        mode = 2
+        mode = 2 if gate is not None else 0   # (no gate: the products alone; a gate per head was applied by the attention already)
         if o_lat.dtype == torch.bfloat16 and self.use_cublas and N >= self.head_matmul_library_rows:
             torch.bmm(o_lat.view(N, num_heads, kv_rank).transpose(0, 1), w_uv.view(num_heads, kv_rank, v_head_dim),
                       out=out.view(N, num_heads, v_head_dim).transpose(0, 1))
             self.launches += 1
+            if gate is None:
+                return out
             mode = 4   # the kernel only multiplies by the gate
+        if gate is None:
+            self._check(self.lib.llmie_head_matmul(_ptr(o_lat), o_lat.shape[1], kv_rank, _ptr(w_uv), _ptr(out), out.shape[1], v_head_dim, N,
+                                                   num_heads, kv_rank, v_head_dim, mode, 0, 0, _ptr(None), _ptr(None), _ptr(None), 0,
+                                                   self._dt(o_lat, "o_lat"), self._stream()), "latent_expand")
+            return out
         self._check(self.lib.llmie_head_matmul(_ptr(o_lat), o_lat.shape[1], kv_rank, _ptr(w_uv), _ptr(out), out.shape[1], v_head_dim, N,
                                                num_heads, kv_rank, v_head_dim, mode, 0, 0, _ptr(None), _ptr(None),
                                                ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1],

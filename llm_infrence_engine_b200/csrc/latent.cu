@@ -23,11 +23,13 @@ __global__ void latent_prepare_kernel(const T* __restrict__ z, int z_stride, int
     pdl_wait();
     const int n = blockIdx.x;
     const T* row = z + (size_t)n * z_stride;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float v = to_f32(row[i]); ss = fmaf(v, v, ss); }
-    ss = block_sum(ss, scratch);
-    float rstd = 1.0f / sqrtf(ss / (float)q_rank + eps);
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[(size_t)n * q_rank + i] = from_f32<T>(to_f32(row[i]) * rstd * wq[i]);
+    float ss = 0.f, rstd;
+    if (q_rank > 0) {   // (q_rank 0: the queries are not made from a latent; only the cache row is written)
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float v = to_f32(row[i]); ss = fmaf(v, v, ss); }
+        ss = block_sum(ss, scratch);
+        rstd = 1.0f / sqrtf(ss / (float)q_rank + eps);
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[(size_t)n * q_rank + i] = from_f32<T>(to_f32(row[i]) * rstd * wq[i]);
+    }
     if (!write) return;
     const T* c = row + q_rank;
     ss = 0.f;
@@ -162,7 +164,7 @@ LLMIE_API int llmie_latent_prepare(const void* z, int z_stride, int q_rank, int 
                                    const float* wkv, float eps, const float* cos_t, const float* sin_t, const int* slots, void* pool,
                                    int page_size, int write, void* cq, int N, int dtype, cudaStream_t s) {
     if (N <= 0) return 0;
-    if (q_rank < 1 || kv_rank < 1 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && (!cos_t || !sin_t)) ||
+    if (q_rank < 0 || (q_rank && (!wq || !cq)) || kv_rank < 1 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || (rot_dims && (!cos_t || !sin_t)) ||
         (write && (!slots || !pool)))
         return LLMIE_ERR_BAD_ARGUMENT;
     if (dtype == DT_F32)

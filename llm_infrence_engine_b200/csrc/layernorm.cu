@@ -37,10 +37,11 @@ __device__ __forceinline__ void row_stats(const float* buf, int H, int step, flo
     rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
 }
 
+// post_plain: the sublayer's result is not normed before it is added, only scaled element by element: x <- x + y * w_post (a layer scale).
 template <typename TY, typename TO, int VEC>
 __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, const float* __restrict__ w_post, int clear_y,
                                  const float* __restrict__ w_pre, const float* __restrict__ b_pre, TO* __restrict__ out,
-                                 const int* __restrict__ rows, int H, float eps) {
+                                 const int* __restrict__ rows, int H, float eps, int post_plain) {
     extern __shared__ __align__(16) float ln_buf[];   // the row of x, the row of y, both weights (H floats each), 100 for the reductions
     float* x_buf = ln_buf;
     float* y_buf = x_buf + H;
@@ -75,8 +76,8 @@ __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, cons
         }
     }
     if (yr) {
-        float mean, rstd;
-        row_stats<VEC>(y_buf, H, step, eps, scratch, mean, rstd);
+        float mean = 0.f, rstd = 1.f;
+        if (!post_plain) row_stats<VEC>(y_buf, H, step, eps, scratch, mean, rstd);
         for (int i = threadIdx.x * VEC; i < H; i += step) {
             float v[VEC], u[VEC], w[VEC];
             if constexpr (VEC == 4) { load4(x_buf + i, v); load4(y_buf + i, u); load4(wp_buf + i, w); } else { v[0] = x_buf[i]; u[0] = y_buf[i]; w[0] = wp_buf[i]; }
@@ -105,7 +106,7 @@ __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, cons
 
 template <typename TY, typename TO>
 int launch_layernorm(float* x, void* y, const float* w_post, int clear_y, const float* w_pre, const float* b_pre, void* out, const int* rows,
-                     int n_out, int H, float eps, cudaStream_t s) {
+                     int n_out, int H, float eps, int post_plain, cudaStream_t s) {
     const size_t smem = (size_t)(4 * H + 100) * sizeof(float);
     const bool vec = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
                      ((uintptr_t)w_post % 16 == 0) && ((uintptr_t)w_pre % 16 == 0);
@@ -114,10 +115,10 @@ int launch_layernorm(float* x, void* y, const float* w_post, int clear_y, const 
     while (threads < 512 && threads * per * 2 <= H) threads *= 2;
     if (vec) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TY, TO, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return launch_kernel(layernorm_kernel<TY, TO, 4>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, b_pre, (TO*)out, rows, H, eps);
+        return launch_kernel(layernorm_kernel<TY, TO, 4>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, b_pre, (TO*)out, rows, H, eps, post_plain);
     }
     if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TY, TO, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_kernel(layernorm_kernel<TY, TO, 1>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, b_pre, (TO*)out, rows, H, eps);
+    return launch_kernel(layernorm_kernel<TY, TO, 1>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, b_pre, (TO*)out, rows, H, eps, post_plain);
 }
 
 // Root-mean-square norm over groups of `gs` consecutive channels, with a gate, one block per (row, group):
@@ -252,12 +253,12 @@ LLMIE_API int llmie_weighted_pair(void* a, int a_dtype, void* b, int b_dtype, fl
 }
 
 LLMIE_API int llmie_layernorm(float* x, void* y, int y_dtype, const float* w_post, int clear_y, const float* w_pre, const float* b_pre, void* out,
-                              int out_dtype, const int* rows, int n_out, int H, float eps, cudaStream_t s) {
+                              int out_dtype, const int* rows, int n_out, int H, float eps, int post_plain, cudaStream_t s) {
     if (n_out <= 0) return 0;
     if (H <= 0 || (size_t)(4 * H + 100) * sizeof(float) > 200 * 1024 || (y && !w_post) || (w_pre && !out)) return LLMIE_ERR_BAD_ARGUMENT;
-    if (y_dtype == DT_F32 && out_dtype == DT_F32) return launch_layernorm<float, float>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, s);
-    if (y_dtype == DT_F32 && out_dtype == DT_BF16) return launch_layernorm<float, bf16>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, s);
-    if (y_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_layernorm<bf16, bf16>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, s);
+    if (y_dtype == DT_F32 && out_dtype == DT_F32) return launch_layernorm<float, float>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, post_plain, s);
+    if (y_dtype == DT_F32 && out_dtype == DT_BF16) return launch_layernorm<float, bf16>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, post_plain, s);
+    if (y_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_layernorm<bf16, bf16>(x, y, w_post, clear_y, w_pre, b_pre, out, rows, n_out, H, eps, post_plain, s);
     return LLMIE_ERR_BAD_ARGUMENT;
 }
 

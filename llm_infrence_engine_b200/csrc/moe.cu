@@ -22,8 +22,9 @@ constexpr int SORT_MAX_EXPERTS = 4096;
 // One warp per token: s = softmax(logits) over all `total` router outputs; the `top` outputs with the largest s + correction are
 // chosen (of equal scores the lower index first); their weights are s / (sum of the chosen s + 1e-20).
 // (one warp: token n's row of logits, in global or shared memory)
+// `scoring` 1 instead: s = sigmoid(logits), every output by itself, and the weights are the chosen s as they are (not renormalised).
 __device__ __forceinline__ void route_token(const float* __restrict__ row, const float* __restrict__ correction, int* __restrict__ ids,
-                                            float* __restrict__ weights, int n, int total, int top, int lane) {
+                                            float* __restrict__ weights, int n, int total, int top, int lane, int scoring) {
     float s[ROUTE_MAX_PER_LANE], c[ROUTE_MAX_PER_LANE];
     float mx = -INFINITY;
 #pragma unroll
@@ -37,10 +38,11 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, const
 #pragma unroll
     for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
         const int e = lane + 32 * j;
-        s[j] = e < total ? expf(s[j] - mx) : 0.f;
+        if (scoring == 1) s[j] = e < total ? 1.0f / (1.0f + expf(-s[j])) : 0.f;
+        else s[j] = e < total ? expf(s[j] - mx) : 0.f;
         sum += s[j];
     }
-    sum = warp_sum(sum);
+    sum = scoring == 1 ? 1.f : warp_sum(sum);
 #pragma unroll
     for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
         const int e = lane + 32 * j;
@@ -78,17 +80,17 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, const
         }
     }
     __syncwarp();
-    const float inv = 1.0f / (chosen_sum + 1e-20f);
+    const float inv = scoring == 1 ? 1.0f : 1.0f / (chosen_sum + 1e-20f);
     for (int k = lane; k < top; k += 32) weights[(size_t)n * top + k] *= inv;
 }
 
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
-                                                        int* __restrict__ ids, float* __restrict__ weights, int N, int total, int top) {
+                                                        int* __restrict__ ids, float* __restrict__ weights, int N, int total, int top, int scoring) {
     pdl_trigger();
     pdl_wait();
     const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (n >= N) return;
-    route_token(logits + (size_t)n * total, correction, ids, weights, n, total, top, threadIdx.x & 31);
+    route_token(logits + (size_t)n * total, correction, ids, weights, n, total, top, threadIdx.x & 31, scoring);
 }
 
 // The router's product and its choice in one kernel, a block per token: the token's row lies in shared memory as floats, the warps
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 constexpr int ROUTER_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ correction,
-                                                                    int* __restrict__ ids, float* __restrict__ weights, int K, int total, int top) {
+                                                                    int* __restrict__ ids, float* __restrict__ weights, int K, int total, int top, int scoring) {
     extern __shared__ __align__(16) float router_smem[];   // [K] the row, then [total] the logits
     constexpr int VN = Vec16<T>::N;
     float* row = router_smem;
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const T* __r
         if (lane == 0) logits[e] = acc;
     }
     __syncthreads();
-    if (warp == 0) route_token(logits, correction, ids, weights, n, total, top, lane);
+    if (warp == 0) route_token(logits, correction, ids, weights, n, total, top, lane, scoring);
 }
 
 // One block: the step's (token, choice) pairs counted per expert, the experts' runs laid out one behind the other, every pair
@@ -190,14 +192,16 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x));
 // most MOE_TM) places of one expert, whose rows of K numbers lie in shared memory as floats; a block owns MOE_COLS outputs, a warp
 // MOE_COLS / 8 of them, taken together: the lanes walk the outputs' weight rows (and, GATED, the up rows of the same outputs)
 // 16 bytes at a time, so the matrices are read once per tile in full lines, which is what bounds a decode step.
-//   GATED: out[place, j] = silu(a . Wg[e][j]) * (a . Wu[e][j]) with W [E][2 F][K] (an expert's gate rows, then its up rows), out of type TO
+//   GATED: out[place, j] = silu(a . Wg[e][j]) * (a . Wu[e][j]) with W [E][2 F][K] (an expert's gate rows, then its up rows), out of type TO;
+//          with limit > 0 the unit is min(g, limit) * sigmoid(alpha g) * (clamp(u, -limit, limit) + shift);
+//          with row_scale the row a is first multiplied by row_scale[pair] (a weight on the expert's input, rounded as it would be stored)
 //   else:  out[place, j] = a . W[e][j] with W [E][F][K]
 // The row a of a place is x[row_map[place] / row_div] (the token of the pair that sits there), or x[place] without a map.
 // A sum runs over K in one order whatever the tile holds: a place's result does not depend on its neighbours.
 template <typename T, typename TO, bool GATED>
 __global__ void __launch_bounds__(256, 2) moe_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_map, int row_div, const T* __restrict__ w,
                                                        const int* __restrict__ offsets, const int* __restrict__ tiles, TO* __restrict__ out, int F,
-                                                       int K, int tile_rows) {
+                                                       int K, int tile_rows, const float* __restrict__ row_scale, float limit, float alpha, float shift) {
     extern __shared__ __align__(16) float moe_rows_smem[];   // [tile_rows][K]
     constexpr int VN = Vec16<T>::N;
     pdl_trigger();
@@ -209,16 +213,17 @@ __global__ void __launch_bounds__(256, 2) moe_rows_kernel(const T* __restrict__ 
     for (int r = 0; r < count; ++r) {
         const int p = p0 + r;
         const T* src = x + (size_t)(row_map ? row_map[p] / row_div : p) * K;
+        const float rs = (row_scale && row_map) ? row_scale[row_map[p]] : 1.f;   // the pair's weight on the expert's INPUT
         float* dst = moe_rows_smem + (size_t)r * K;
         if (vec) {
             for (int k = threadIdx.x * VN; k < K; k += 256 * VN) {
                 float v[VN];
                 Vec16<T>::load(src + k, v);
 #pragma unroll
-                for (int i = 0; i < VN; ++i) dst[k + i] = v[i];
+                for (int i = 0; i < VN; ++i) dst[k + i] = row_scale ? round_through<T>(v[i] * rs) : v[i];
             }
         } else {
-            for (int k = threadIdx.x; k < K; k += 256) dst[k] = to_f32(src[k]);
+            for (int k = threadIdx.x; k < K; k += 256) dst[k] = row_scale ? round_through<T>(to_f32(src[k]) * rs) : to_f32(src[k]);
         }
     }
     __syncthreads();
@@ -289,23 +294,47 @@ __global__ void __launch_bounds__(256, 2) moe_rows_kernel(const T* __restrict__ 
             for (int c = 0; c < CPW; ++c) {
                 const float sg = warp_sum(ag[c][r]);
                 const float su = GATED ? warp_sum(au[GATED ? c : 0][r]) : 0.f;
-                if (lane == 0 && j0 + c < F) out[(size_t)(p0 + r) * F + j0 + c] = from_f32<TO>(GATED ? silu_f(sg) * su : sg);
+                float res = sg;
+                if (GATED) {
+                    if (limit > 0.f) {   // the clamped unit
+                        const float g = fminf(sg, limit), u = fminf(fmaxf(su, -limit), limit) + shift;
+                        res = g / (1.0f + expf(-alpha * g)) * u;
+                    } else {
+                        res = silu_f(sg) * su;
+                    }
+                }
+                if (lane == 0 && j0 + c < F) out[(size_t)(p0 + r) * F + j0 + c] = from_f32<TO>(res);
             }
         }
     }
 }
 
-// xs[place] = x[perm[place] / top] for the places that the sort filled (offsets[E] of them): the rows of the tokens, in the order
+// xs[place] = x[perm[place] / top] (times row_scale[perm[place]], where given) for the places that the sort filled (offsets[E] of them): the rows of the tokens, in the order
 // of their experts, as the tensor-core grouped product reads them. One block per place.
 __global__ void moe_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ perm, const int* __restrict__ offsets, int E, int top,
-                                  bf16* __restrict__ xs, int K) {
+                                  bf16* __restrict__ xs, int K, const float* __restrict__ row_scale) {
     pdl_trigger();
     pdl_wait();
     const int p = blockIdx.x;
     if (p >= offsets[E]) return;
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(perm[p] / top) * K);
     uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)p * K);
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+    if (!row_scale) {
+        for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+        return;
+    }
+    const float rs = row_scale[perm[p]];   // the pair's weight on the expert's input
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+        float v[8];
+        Vec16<bf16>::load(reinterpret_cast<const bf16*>(src + i), v);
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * j] * rs, v[2 * j + 1] * rs);
+            w[j] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
 }
 
 // residual[t] += sum_k weight[t, k] * (y[place_of[t, k]] for an expert with matrices, h[t] itself for an identity expert), the
@@ -322,7 +351,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(float* __restrict__ re
     float sum[COMBINE_VEC] = {};
     for (int k = 0; k < top; ++k) {
         const int p = place_of[(size_t)t * top + k];
-        const float wk = weights[(size_t)t * top + k];
+        const float wk = weights ? weights[(size_t)t * top + k] : 1.f;   // (no weights: they were put on the experts' inputs)
         float v[COMBINE_VEC];
         if (p >= 0) {
             if (COMBINE_VEC == 4) {
@@ -350,16 +379,17 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(float* __restrict__ re
 
 }  // namespace
 
-LLMIE_API int llmie_moe_route(const float* logits, const float* correction, int* ids, float* weights, int N, int total, int top, cudaStream_t s) {
+LLMIE_API int llmie_moe_route(const float* logits, const float* correction, int* ids, float* weights, int N, int total, int top, int scoring,
+                              cudaStream_t s) {
     if (N <= 0) return 0;
     if (total <= 0 || total > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > total) return LLMIE_ERR_BAD_ARGUMENT;
-    return launch_kernel(moe_route_kernel, dim3((N + 3) / 4), dim3(128), 0, s, logits, correction, ids, weights, N, total, top);
+    return launch_kernel(moe_route_kernel, dim3((N + 3) / 4), dim3(128), 0, s, logits, correction, ids, weights, N, total, top, scoring);
 }
 
 // ids, weights [N, top] from the rows h [N, K] and the router's matrix w [total, K] of the same type (float or bfloat16): the product in
 // 32-bit and the choice, one launch. The row and the logits must fit the shared memory (K + total floats: up to about 50,000).
 LLMIE_API int llmie_moe_router(const void* h, const void* w, const float* correction, int* ids, float* weights, int N, int K, int total, int top,
-                               int dtype, cudaStream_t s) {
+                               int scoring, int dtype, cudaStream_t s) {
     if (N <= 0) return 0;
     if (K <= 0 || total <= 0 || total > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > total) return LLMIE_ERR_BAD_ARGUMENT;
     const size_t smem = ((size_t)((K + 3) & ~3) + total) * sizeof(float);
@@ -372,7 +402,7 @@ LLMIE_API int llmie_moe_router(const void* h, const void* w, const float* correc
             allowed_f = 200 * 1024;
         }
         return launch_kernel(moe_router_kernel<float>, dim3(N), dim3(ROUTER_THREADS), smem, s, (const float*)h, (const float*)w, correction, ids, weights, K,
-                             total, top);
+                             total, top, scoring);
     }
     if (smem > allowed_b) {
         cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -380,7 +410,7 @@ LLMIE_API int llmie_moe_router(const void* h, const void* w, const float* correc
         allowed_b = 200 * 1024;
     }
     return launch_kernel(moe_router_kernel<bf16>, dim3(N), dim3(ROUTER_THREADS), smem, s, (const bf16*)h, (const bf16*)w, correction, ids, weights, K, total,
-                         top);
+                         top, scoring);
 }
 
 // Rows per tile of the grouped product on the CUDA cores for rows of K numbers: as many as fit the shared memory, at most MOE_TM;
@@ -401,7 +431,7 @@ LLMIE_API int llmie_moe_sort(const int* ids, int pairs, int E, int tile_rows, in
 
 template <typename T, typename TO, bool GATED>
 static int launch_moe_rows(const void* x, const int* row_map, int row_div, const void* w, const int* offsets, const int* tiles, int max_tiles, void* out,
-                           int F, int K, int tile_rows, cudaStream_t s) {
+                           int F, int K, int tile_rows, const float* row_scale, float limit, float alpha, float shift, cudaStream_t s) {
     const size_t smem = (size_t)tile_rows * K * sizeof(float);
     static size_t allowed = 48 * 1024;
     if (smem > allowed) {
@@ -411,29 +441,32 @@ static int launch_moe_rows(const void* x, const int* row_map, int row_div, const
     }
     const dim3 grid((F + MOE_COLS - 1) / MOE_COLS, max_tiles);
     return launch_kernel(moe_rows_kernel<T, TO, GATED>, grid, dim3(256), smem, s, (const T*)x, row_map, row_div, (const T*)w, offsets, tiles, (TO*)out, F, K,
-                         tile_rows);
+                         tile_rows, row_scale, limit, alpha, shift);
 }
 
 // gated != 0: w [E][2 F][K], out [places][F] of the storage type; else w [E][F][K], out [places][F] float. tile_rows as given to the sort.
+// row_scale [pairs] or null: a weight on every pair's input row (needs row_map); limit > 0: the clamped unit (see the kernel).
 LLMIE_API int llmie_moe_gemm(const void* x, const int* row_map, int row_div, const void* w, const int* offsets, const int* tiles, int max_tiles,
-                             void* out, int F, int K, int gated, int tile_rows, int dtype, cudaStream_t s) {
+                             void* out, int F, int K, int gated, int tile_rows, const float* row_scale, float limit, float alpha, float shift, int dtype,
+                             cudaStream_t s) {
     if (max_tiles <= 0) return 0;
     if (F <= 0 || K <= 0 || max_tiles > 65535 || (row_map && row_div <= 0) || tile_rows <= 0 || tile_rows > MOE_TM || tile_rows > llmie_moe_tile_rows(K))
         return LLMIE_ERR_BAD_ARGUMENT;
     if (dtype == DT_F32) {
-        if (gated) return launch_moe_rows<float, float, true>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, s);
-        return launch_moe_rows<float, float, false>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, s);
+        if (gated) return launch_moe_rows<float, float, true>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, row_scale, limit, alpha, shift, s);
+        return launch_moe_rows<float, float, false>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, row_scale, limit, alpha, shift, s);
     }
-    if (gated) return launch_moe_rows<bf16, bf16, true>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, s);
-    return launch_moe_rows<bf16, float, false>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, s);
+    if (gated) return launch_moe_rows<bf16, bf16, true>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, row_scale, limit, alpha, shift, s);
+    return launch_moe_rows<bf16, float, false>(x, row_map, row_div, w, offsets, tiles, max_tiles, out, F, K, tile_rows, row_scale, limit, alpha, shift, s);
 }
 
 // xs [pairs][K] bfloat16 (K a multiple of 8, 16-byte aligned rows): the tokens' rows in the order of the sort.
-LLMIE_API int llmie_moe_gather(const void* x, const int* perm, const int* offsets, int E, int top, void* xs, int pairs, int K, cudaStream_t s) {
+LLMIE_API int llmie_moe_gather(const void* x, const int* perm, const int* offsets, int E, int top, void* xs, int pairs, int K, const float* row_scale,
+                               cudaStream_t s) {
     if (pairs <= 0) return 0;
     if (K <= 0 || K % 8 || top <= 0 || ((uintptr_t)x & 15) || ((uintptr_t)xs & 15)) return LLMIE_ERR_BAD_ARGUMENT;
     return launch_kernel(moe_gather_kernel, dim3(pairs), dim3(K / 8 < 256 ? (K / 8 < 32 ? 32 : K / 8) : 256), 0, s, (const bf16*)x, perm, offsets, E, top,
-                         (bf16*)xs, K);
+                         (bf16*)xs, K, row_scale);
 }
 
 LLMIE_API int llmie_moe_combine(float* residual, const float* y, const void* h, const int* place_of, const float* weights, int N, int top, int W,

@@ -28,7 +28,7 @@ constexpr int EPI_THREADS = 128, THREADS = 64 + EPI_THREADS;
 template <bool GATED>
 __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                                                                   const int* __restrict__ offsets, const int* __restrict__ tile_list, void* __restrict__ out_,
-                                                                  int F, int K, int* error_flag) {
+                                                                  int F, int K, int* error_flag, float limit, float alpha, float shift) {
     constexpr int ACC_COLS = 2 * BN;                              // columns of tensor memory per accumulator
     constexpr int TILE_N = GATED ? BN : 2 * BN;                   // outputs per tile
     constexpr int B_BYTES = ACC_COLS * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -141,9 +141,16 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_co
                     uint32_t packed[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const float g0 = __uint_as_float(gv[2 * j]), g1 = __uint_as_float(gv[2 * j + 1]);
-                        const float u0 = __uint_as_float(uv[2 * j]), u1 = __uint_as_float(uv[2 * j + 1]);
-                        const __nv_bfloat162 v = __floats2bfloat162_rn(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+                        float g0 = __uint_as_float(gv[2 * j]), g1 = __uint_as_float(gv[2 * j + 1]);
+                        float u0 = __uint_as_float(uv[2 * j]), u1 = __uint_as_float(uv[2 * j + 1]);
+                        float a0 = 1.0f;
+                        if (limit > 0.f) {   // the clamped unit: min(g, limit) * sigmoid(alpha g) * (clamp(u) + shift)
+                            g0 = fminf(g0, limit); g1 = fminf(g1, limit);
+                            u0 = fminf(fmaxf(u0, -limit), limit) + shift;
+                            u1 = fminf(fmaxf(u1, -limit), limit) + shift;
+                            a0 = alpha;
+                        }
+                        const __nv_bfloat162 v = __floats2bfloat162_rn(__fdividef(g0, 1.0f + __expf(-a0 * g0)) * u0, __fdividef(g1, 1.0f + __expf(-a0 * g1)) * u1);
                         packed[j] = *reinterpret_cast<const uint32_t*>(&v);
                     }
                     if (mine) {
@@ -188,7 +195,7 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_tc_kernel(const __grid_co
 
 template <bool GATED>
 int launch_grouped(const bf16* a, int places, const bf16* w, int E, const int* offsets, const int* tile_list, int max_tiles, void* out, int F, int K,
-                   int num_blocks, int* error_flag, cudaStream_t s) {
+                   int num_blocks, int* error_flag, float limit, float alpha, float shift, cudaStream_t s) {
     CUtensorMap ma, mw;
     int rc = tensor_map(a, places, K, BM, &ma);
     if (rc) return rc;
@@ -203,7 +210,7 @@ int launch_grouped(const bf16* a, int places, const bf16* w, int E, const int* o
     }
     const long long most = (long long)max_tiles * ((F + (GATED ? BN : 2 * BN) - 1) / (GATED ? BN : 2 * BN));
     const int grid = (int)(most < num_blocks ? most : num_blocks);
-    return launch_kernel(moe_grouped_tc_kernel<GATED>, dim3(grid), dim3(THREADS), smem, s, ma, mw, offsets, tile_list, out, F, K, error_flag);
+    return launch_kernel(moe_grouped_tc_kernel<GATED>, dim3(grid), dim3(THREADS), smem, s, ma, mw, offsets, tile_list, out, F, K, error_flag, limit, alpha, shift);
 }
 
 }  // namespace
@@ -214,12 +221,13 @@ LLMIE_API int llmie_moe_grouped_tc_rows() { return BM; }
 // a [places, K] bfloat16 (rows in the order of the places), w [E][gated ? 2 F : F][K] bfloat16, offsets [E + 1] and tile_list
 // [1 + 2 max_tiles] on the device as the sort leaves them (tiles of up to 128 places); out [places, F]: bfloat16 with `gated`,
 // float32 without. K and F multiples of 8, bases 16-byte aligned. num_blocks: the persistent grid (the number of multiprocessors).
+// limit > 0 (with `gated`): the unit is min(g, limit) * sigmoid(alpha g) * (clamp(u, -limit, limit) + shift) instead of silu(g) * u.
 LLMIE_API int llmie_moe_grouped_tc(const bf16* a, int places, const bf16* w, int E, const int* offsets, const int* tile_list, int max_tiles, void* out,
-                                    int F, int K, int gated, int num_blocks, int* error_flag, cudaStream_t s) {
+                                    int F, int K, int gated, int num_blocks, int* error_flag, float limit, float alpha, float shift, cudaStream_t s) {
     if (places <= 0 || max_tiles <= 0) return 0;
     if (E <= 0 || F <= 0 || K <= 0 || K % 8 || F % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || !error_flag ||
         num_blocks < 1 || (long long)E * 2 * F > 0x7fffffffLL)
         return LLMIE_ERR_BAD_ARGUMENT;
-    if (gated) return launch_grouped<true>(a, places, w, E, offsets, tile_list, max_tiles, out, F, K, num_blocks, error_flag, s);
-    return launch_grouped<false>(a, places, w, E, offsets, tile_list, max_tiles, out, F, K, num_blocks, error_flag, s);
+    if (gated) return launch_grouped<true>(a, places, w, E, offsets, tile_list, max_tiles, out, F, K, num_blocks, error_flag, limit, alpha, shift, s);
+    return launch_grouped<false>(a, places, w, E, offsets, tile_list, max_tiles, out, F, K, num_blocks, error_flag, 0.f, 1.f, 0.f, s);
 }

@@ -404,6 +404,8 @@ class ModelRunner:
             b = self.bindings[call.cache]
             if not call.write:
                 b = _read_only(b)
+            if call.add_embedding:
+                spec.embedding.add_into(ctx, residual)
             spec.layers[call.layer].forward(ctx, residual, b)
         if logit_rows.numel() == 0:
             if hasattr(self.K, "flush"):

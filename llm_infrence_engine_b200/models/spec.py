@@ -14,12 +14,14 @@ class LayerCall:
 
     A layer may be named by several calls (its weights run again), each with a cache entry of its
     own; and a call with ``write=False`` reads a cache entry that an earlier call filled instead
-    of keeping one itself.
+    of keeping one itself. A call with ``add_embedding`` opens a further pass over layers that ran before: the stream gets
+    the tokens' embedding added again first.
     """
 
     layer: int
     cache: int
     write: bool = True
+    add_embedding: bool = False   # the embedding of the step's tokens is added into the stream once more right before this call
 
 
 @dataclass
@@ -40,6 +42,8 @@ class ModelSpec:
 
     def cache_specs(self) -> list:
         """The spec of every cache entry, taken from the call that writes it."""
+        if self.streams is not None and any(c.add_embedding for c in self.schedule):
+            raise ValueError("the embedding is added again into one residual stream only, not into several")
         n = 1 + max((c.cache for c in self.schedule), default=-1)
         specs: list = [None] * n
         written = [False] * n

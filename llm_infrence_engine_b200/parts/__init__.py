@@ -9,10 +9,10 @@ from .embedding import OutputHead, TokenEmbedding
 from .hyper import HyperConnection, HyperConnectionBlock, ResidualStreams
 from .mlp import ClampedGLU, DenseMLP, GatedMLP, GatedUnit, RoutedExperts
 from .norm import LayerNorm, RMSNorm
-from .recurrent import GatedDeltaMixer, HeadDecayDeltaMixer, ParallelMixer, SelectiveScanMixer, StateSpaceMixer
+from .recurrent import GatedDeltaMixer, HeadDecayDeltaMixer, MatrixMemoryMixer, ParallelMixer, SelectiveScanMixer, StateSpaceMixer
 from .rotary import RampedRotary, RotaryEncoding
 
-__all__ = ["MaskedAttention", "SandwichBlock", "ParallelBlock", "GatedUnit", "RoutedExperts", "HeadDecayDeltaMixer", "SelectiveScanMixer", "ClampedGLU", "LayerNorm", "GatedDeltaMixer", "ParallelMixer", "StateSpaceMixer", "RampedRotary",
+__all__ = ["MatrixMemoryMixer", "MaskedAttention", "SandwichBlock", "ParallelBlock", "GatedUnit", "RoutedExperts", "HeadDecayDeltaMixer", "SelectiveScanMixer", "ClampedGLU", "LayerNorm", "GatedDeltaMixer", "ParallelMixer", "StateSpaceMixer", "RampedRotary",
            "PagedAttention", "BiasedAttention", "LatentAttention", "HyperConnection", "HyperConnectionBlock", "ResidualStreams", "DenseMLP", "FeedForward", "Mixer", "Norm", "ParamSpec", "Part", "PositionEncoding", "Source", "walk",
            "PreNormBlock", "OutputHead", "TokenEmbedding", "GatedMLP", "RMSNorm", "RotaryEncoding",
            "ANY", "INIT_EYE", "INIT_NORM", "INIT_NORMAL", "INIT_ONES", "INIT_SHARE", "INIT_SMALL", "MATRIX", "TABLE", "VECTOR"]

@@ -1,11 +1,11 @@
 """One layer: how norms, mixer and feed-forward are arranged around the residual stream."""
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, Part
+from .base import INIT_NORM, VECTOR, FeedForward, Mixer, Norm, ParamSpec, Part, Source
 
 
 class PreNormBlock(Part):
@@ -14,14 +14,34 @@ class PreNormBlock(Part):
     The residual stream ``x`` is 32-bit and is updated in place: the mixer and the feed-forward are handed
     ``x`` and add their result into it themselves, which lets their last matrix product do the addition
     in its own epilogue instead of a kernel of its own.
+
+    With a layer scale (``scale1`` / ``scale2`` name vectors of ``dim`` entries): ``x += scale1 * mixer(norm1(x))`` and
+    ``x += scale2 * ff(norm2(x))``, element by element. The sublayer then adds its result into a zeroed tensor as it would into the
+    stream, and the scaled addition is put off until the next norm of the stream, whose kernel adds and normalises in one pass.
     """
 
     graph_safe = True
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None, ff: Optional[FeedForward] = None):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None, ff: Optional[FeedForward] = None,
+                 scale1: Optional[str] = None, scale2: Optional[str] = None, dim: int = 0):
         if (norm2 is None) != (ff is None):
             raise ValueError("a feed-forward comes with its norm, or neither is there")
+        if (scale1 or scale2) and dim <= 0:
+            raise ValueError("a layer scale needs the width of the stream")
+        if scale2 and ff is None:
+            raise ValueError("a layer scale of the feed-forward needs a feed-forward")
         self.norm1, self.mixer, self.norm2, self.ff = norm1, mixer, norm2, ff
+        self.scale1_name, self.scale2_name, self.dim = scale1, scale2, int(dim)
+        self.scale1: Optional[torch.Tensor] = None
+        self.scale2: Optional[torch.Tensor] = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        out = {}
+        if self.scale1_name:
+            out["scale1"] = ParamSpec((Source(self.scale1_name, (self.dim,), INIT_NORM),), VECTOR)
+        if self.scale2_name:
+            out["scale2"] = ParamSpec((Source(self.scale2_name, (self.dim,), INIT_NORM),), VECTOR)
+        return out
 
     def children(self) -> Sequence[Part]:
         return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ff) if p is not None)
@@ -30,9 +50,22 @@ class PreNormBlock(Part):
         return self.mixer.cache_spec()
 
     def forward(self, ctx, residual: torch.Tensor, cache) -> None:
-        self.mixer.forward(ctx, self.norm1.norm(ctx, residual), cache, residual)
+        K = ctx.K
+        h = self.norm1.norm(ctx, residual)
+        if self.scale1 is None:
+            self.mixer.forward(ctx, h, cache, residual)
+        else:
+            y = K.zeros_like_rows(residual)
+            self.mixer.forward(ctx, h, cache, y)
+            K.scaled_add(residual, y, self.scale1)
         if self.ff is not None:   # a layer may be a mixer alone
-            self.ff.forward(ctx, self.norm2.norm(ctx, residual), residual)
+            h = self.norm2.norm(ctx, residual)
+            if self.scale2 is None:
+                self.ff.forward(ctx, h, residual)
+            else:
+                y = K.zeros_like_rows(residual)
+                self.ff.forward(ctx, h, y)
+                K.scaled_add(residual, y, self.scale2)
 
 
 class SandwichBlock(Part):

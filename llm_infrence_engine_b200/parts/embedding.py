@@ -26,6 +26,10 @@ class TokenEmbedding(Part):
             return ctx.K.embed(ctx.token_ids, self.table)
         return ctx.K.embed(ctx.token_ids, self.table, self.scale)
 
+    def add_into(self, ctx, residual: torch.Tensor) -> None:
+        """``residual += table[token] * scale``: the step's embedding once more, for a model that feeds it in again on the way."""
+        ctx.K.embed_add(ctx.token_ids, self.table, residual, self.scale)
+
 
 class OutputHead(Part):
     """``logits = h W^T`` without bias, in 32-bit. ``tied_to`` makes ``W`` the embedding's own table

@@ -125,16 +125,31 @@ class RoutedExperts(FeedForward):
     input back from it (times the weight). ``shared`` (a feed-forward of its own, or None) runs for every token and is added.
     Checkpoint names: ``{prefix}.router``, ``{prefix}.correction``, ``{prefix}.e<i>.gate / up / down``. The experts' matrices are
     kept stacked (``[E, 2 ff, hidden]`` and ``[E, hidden, ff]``); tokens are sorted by expert on the device and every expert's
-    rows pass its matrices in one grouped product, so the part only launches kernels."""
+    rows pass its matrices in one grouped product, so the part only launches kernels.
+
+    Other routers and experts, each a constructor argument:
+
+    * ``scoring="sigmoid"``: ``s = sigmoid(W_router x)``, every output by itself, and the weights are the chosen ``s`` as they are;
+    * ``correction=False``: no correction vector in the checkpoint;
+    * ``weight_inputs``: the weight multiplies the expert's INPUT, the output is ``sum_k expert(w_k x)``;
+    * ``expert_glu=(limit, alpha, shift)``: the experts are clamped units, ``down(g sigmoid(alpha g) (u + shift))`` with
+      ``g = min(gate x, limit)`` and ``u = clamp(up x, -limit, limit)``."""
 
     graph_safe = True
 
     def __init__(self, hidden: int, intermediate: int, num_experts: int, num_identity: int, top: int, prefix: str,
-                 shared: Optional[FeedForward] = None):
+                 shared: Optional[FeedForward] = None, scoring: str = "softmax", correction: bool = True, weight_inputs: bool = False,
+                 expert_glu: Optional[tuple] = None):
         if not 1 <= top <= num_experts + num_identity:
             raise ValueError(f"{top} of {num_experts + num_identity} router outputs cannot be chosen")
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"a router scores by 'softmax' or 'sigmoid', got {scoring!r}")
+        if weight_inputs and num_identity:
+            raise ValueError("weights on the experts' inputs are not built together with identity experts")
         self.hidden, self.intermediate, self.num_experts, self.num_identity, self.top = hidden, intermediate, num_experts, num_identity, top
         self.prefix, self.shared = prefix, shared
+        self.scoring, self.has_correction, self.weight_inputs = scoring, bool(correction), bool(weight_inputs)
+        self.expert_glu = None if expert_glu is None else tuple(float(v) for v in expert_glu)
         self.w_router = self.correction = self.w_gate_up = self.w_down = None
 
     def children(self):
@@ -144,10 +159,12 @@ class RoutedExperts(FeedForward):
         p, h, i, E = self.prefix, self.hidden, self.intermediate, self.num_experts
         total = E + self.num_identity
         gate_up = tuple(Source(f"{p}.e{e}.{n}", (i, h), INIT_PROJ) for e in range(E) for n in ("gate", "up"))
-        return {"w_router": ParamSpec((Source(f"{p}.router", (total, h), INIT_PROJ),), MATRIX),
-                "correction": ParamSpec((Source(f"{p}.correction", (total,), INIT_SMALL),), VECTOR),
-                "w_gate_up": ParamSpec(gate_up, MATRIX),
-                "w_down": ParamSpec(tuple(Source(f"{p}.e{e}.down", (h, i), INIT_PROJ) for e in range(E)), MATRIX)}
+        out = {"w_router": ParamSpec((Source(f"{p}.router", (total, h), INIT_PROJ),), MATRIX),
+               "w_gate_up": ParamSpec(gate_up, MATRIX),
+               "w_down": ParamSpec(tuple(Source(f"{p}.e{e}.down", (h, i), INIT_PROJ) for e in range(E)), MATRIX)}
+        if self.has_correction:
+            out["correction"] = ParamSpec((Source(f"{p}.correction", (total,), INIT_SMALL),), VECTOR)
+        return out
 
     def bind(self, tensors) -> None:
         super().bind(tensors)
@@ -157,7 +174,11 @@ class RoutedExperts(FeedForward):
 
     def forward(self, ctx, h, residual):
         K = ctx.K
-        ids, weights = K.moe_router(h, self.w_router, self.correction, self.top)
-        K.moe_experts(h, ids, weights, self.w_gate_up, self.w_down, add_to=residual)
+        if self.scoring == "softmax" and not self.weight_inputs and self.expert_glu is None:
+            ids, weights = K.moe_router(h, self.w_router, self.correction, self.top)
+            K.moe_experts(h, ids, weights, self.w_gate_up, self.w_down, add_to=residual)
+        else:
+            ids, weights = K.moe_router(h, self.w_router, self.correction, self.top, scoring=self.scoring)
+            K.moe_experts(h, ids, weights, self.w_gate_up, self.w_down, add_to=residual, glu=self.expert_glu, weight_inputs=self.weight_inputs)
         if self.shared is not None:
             self.shared.forward(ctx, h, residual)

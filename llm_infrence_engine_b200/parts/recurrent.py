@@ -301,6 +301,73 @@ class SelectiveScanMixer(Mixer):
         K.linear(y, self.w_o, add_to=residual)
 
 
+class MatrixMemoryMixer(Mixer):
+    """A matrix memory with exponential gates (the mLSTM cell of xLSTM). Per head, with ``q = W_q x * head_dim^-1/2``, ``k = W_k x``
+    (``head_dim`` entries) and ``v = W_v x`` (``v_head_dim``), a log input gate ``i = cap tanh((W_i x + b_i) / cap)`` and a log forget
+    gate ``f = ln sigmoid(cap tanh((W_f x + b_f) / cap))`` (``gate_cap`` None: no cap), and a running maximum ``m`` that starts at 0:
+
+        m' = max(f + m, i);   S <- exp(f + m - m') S + exp(i - m') k v^T;   n <- the same with k alone;
+        o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+
+    Every head's ``o`` is divided by its root mean square; the heads side by side are multiplied by a weight of ``heads * v_head_dim``
+    entries and by ``sigmoid(W_g x)``; then the output projection. ``S``, ``n`` and ``m`` start at zero and are a request's state (32-bit:
+    the memory column by column with the normaliser as one more column, and ``m``); gates, their logarithms and exponentials are
+    32-bit, made from 32-bit pre-activations (a small product of its own beside the joined projection ``q | k | v | g``).
+    Checkpoint names: ``{prefix}.q / k / v / g / o``, ``.i`` and ``.f`` (+ ``.b``), ``.norm``."""
+
+    graph_safe = True
+
+    def __init__(self, hidden: int, num_heads: int, head_dim: int, v_head_dim: int, gate_cap: Optional[float], eps: float, prefix: str):
+        if head_dim > 256:
+            raise ValueError(f"the memory's kernel keeps a column in registers: head_dim {head_dim} is more than 256")
+        self.hidden, self.num_heads, self.head_dim, self.v_head_dim = hidden, num_heads, head_dim, v_head_dim
+        self.gate_cap = float(gate_cap) if gate_cap else None
+        self.eps, self.prefix = float(eps), prefix
+        self.q_col = self.k_col = self.v_col = self.g_col = 0     # columns of the joined projection's sections: set when the weights are bound
+        self.w_in = self.w_gates = self.w_o = self.bias_i = self.bias_f = self.norm_w = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        p, h, H, D, DV = self.prefix, self.hidden, self.num_heads, self.head_dim, self.v_head_dim
+        return {
+            "w_in": ParamSpec((Source(f"{p}.q", (H * D, h), INIT_PROJ), Source(f"{p}.k", (H * D, h), INIT_PROJ), Source(f"{p}.v", (H * DV, h), INIT_PROJ),
+                               Source(f"{p}.g", (H * DV, h), INIT_PROJ)), MATRIX),
+            "w_gates": ParamSpec((Source(f"{p}.i", (H, h), INIT_PROJ), Source(f"{p}.f", (H, h), INIT_PROJ)), MATRIX),
+            "w_o": ParamSpec((Source(f"{p}.o", (h, H * DV), INIT_PROJ),), MATRIX),
+            "bias_i": ParamSpec((Source(f"{p}.i.b", (H,), INIT_SMALL),), VECTOR),
+            "bias_f": ParamSpec((Source(f"{p}.f.b", (H,), INIT_NORM),), VECTOR),
+            "norm_w": ParamSpec((Source(f"{p}.norm", (H * DV,), INIT_NORM),), VECTOR),
+        }
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_gates, self.w_o, self.bias_i, self.bias_f, self.norm_w) if t is not None)
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        H, D, DV = self.num_heads, self.head_dim, self.v_head_dim
+        # every section of the joined projection starts on a multiple of 8 rows: its columns of the product then start on a 16-byte boundary
+        pieces, starts, at = [], [], 0
+        for part in torch.split(self.w_in, (H * D, H * D, H * DV, H * DV)):
+            starts.append(at)
+            pieces.append(_padded(part))
+            at += pieces[-1].shape[0]
+        self.q_col, self.k_col, self.v_col, self.g_col = starts
+        self.w_in = torch.cat(pieces).contiguous()
+        self.w_gates = _padded(self.w_gates)   # [i | f], then zero rows
+
+    def cache_spec(self):
+        return (FixedStateSpec((self.num_heads, self.v_head_dim + 1, self.head_dim)), FixedStateSpec((self.num_heads,)))   # S and n column by column; m
+
+    def forward(self, ctx, h, cache, residual):
+        K = ctx.K
+        memory, maximum = cache
+        H, D, DV = self.num_heads, self.head_dim, self.v_head_dim
+        z = K.linear(h, self.w_in, out_dtype=ctx.dtype)
+        gates = K.linear(h, self.w_gates, out_dtype=torch.float32)
+        num, m = K.mlstm(z, self.q_col, self.k_col, self.v_col, gates, self.bias_i, self.bias_f, self.gate_cap, H, D, DV, memory.state, maximum.state, ctx)
+        y = K.mlstm_finish(num, m, z, self.g_col, self.norm_w, self.eps, ctx.dtype)
+        K.linear(y, self.w_o, add_to=residual)
+
+
 class ParallelMixer(Mixer):
     """Two mixers side by side on the same input, each with its own cache or state. Two ways of joining their outputs:
 

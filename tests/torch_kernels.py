@@ -23,6 +23,9 @@ class TorchKernels:
     def embed(self, token_ids, table, scale=1.0):
         return table[token_ids.long()].float() * scale
 
+    def embed_add(self, token_ids, table, residual, scale=1.0):
+        residual += table[token_ids.long()].float() * scale
+
     def feed_tokens(self, token_ids, source_rows, previous_tokens):
         take = source_rows >= 0
         token_ids[take] = previous_tokens[source_rows[take].long()]
@@ -170,7 +173,7 @@ class TorchKernels:
 
     def attention_ext(self, q, q_col, num_heads, num_kv_heads, head_dim, v_head_dim, k_pool, v_pool, block_table, token_seq, positions,
                       page_size, scale, window, max_context, temp=(0.0, 0), rel=None, rel_rows=None, sink=None, gate=None, gate_col=0,
-                      gate_per_head=False, batch=None, num_splits=None, keep_first=0, chunk=0, softcap=0.0):
+                      gate_per_head=False, batch=None, num_splits=None, keep_first=0, chunk=0, softcap=0.0, talk=None):
         N = q.shape[0]
         rep = num_heads // num_kv_heads
         qs = q[:, q_col:q_col + num_heads * head_dim].float().view(N, num_heads, head_dim)
@@ -188,10 +191,18 @@ class TorchKernels:
             factor = scale
             if temp[1]:
                 factor = scale * (1.0 + temp[0] * math.log((p + 1) // temp[1] + 1))
+            mixed = None
+            if talk is not None:   # every head's capped scores first, then their mix
+                plain = torch.stack([(k[:, g // rep] @ qs[t, g]) * factor for g in range(num_heads)])
+                if softcap:
+                    plain = softcap * torch.tanh(plain / softcap)
+                mixed = talk.float() @ plain
             for h in range(num_heads):
                 s = (k[:, h // rep] @ qs[t, h]) * factor
                 if softcap:
                     s = softcap * torch.tanh(s / softcap)
+                if mixed is not None:
+                    s = mixed[h]
                 if rel is not None:
                     dist = p - keys
                     row = torch.where(dist < rel_rows.shape[0], rel_rows.long()[dist.clamp(max=rel_rows.shape[0] - 1)], rel.shape[0] - 1)
@@ -224,6 +235,9 @@ class TorchKernels:
 
     def post_norm_add(self, residual, y, weight, eps):
         residual += self._ln(y.float(), weight, eps)
+
+    def scaled_add(self, residual, y, weight):
+        residual += y.float() * weight.float()
 
     def group_rmsnorm_gate(self, x, gate, gate_col, weight, group_size, eps, gate_first, out_dtype, gate_act="sigmoid"):
         N, C = x.shape
@@ -367,29 +381,38 @@ class TorchKernels:
         return out.to(x.dtype)
 
     # ------------------------------------------------------------------ routed experts
-    def moe_route(self, logits, correction, top):
-        s = torch.softmax(logits.float(), dim=-1)
+    def moe_route(self, logits, correction, top, scoring="softmax"):
+        if scoring == "sigmoid":
+            s = torch.sigmoid(logits.float())
+        else:
+            s = torch.softmax(logits.float(), dim=-1)
         choice = s if correction is None else s + correction.float()
         ids = torch.topk(choice, top, dim=-1).indices
         w = torch.gather(s, 1, ids)
-        return ids.to(torch.int32), w / (w.sum(-1, keepdim=True) + 1e-20)
+        return ids.to(torch.int32), w if scoring == "sigmoid" else w / (w.sum(-1, keepdim=True) + 1e-20)
 
-    def moe_router(self, h, w_router, correction, top):
-        return self.moe_route(h.float() @ w_router.float().T, correction, top)
+    def moe_router(self, h, w_router, correction, top, scoring="softmax"):
+        return self.moe_route(h.float() @ w_router.float().T, correction, top, scoring)
 
-    def moe_experts(self, h, ids, weights, w_gate_up, w_down, add_to):
+    def moe_experts(self, h, ids, weights, w_gate_up, w_down, add_to, glu=None, weight_inputs=False):
         E, F = w_gate_up.shape[0], w_gate_up.shape[1] // 2
         x = h.float()
         for t in range(h.shape[0]):
             for k in range(ids.shape[1]):
                 e = int(ids[t, k])
+                xin = (x[t] * weights[t, k]).to(h.dtype).float() if weight_inputs else x[t]
                 if e < E:
-                    gu = w_gate_up[e].float() @ x[t]
-                    act = (gu[:F] * torch.sigmoid(gu[:F]) * gu[F:]).to(h.dtype).float()
-                    y = w_down[e].float() @ act
+                    gu = w_gate_up[e].float() @ xin
+                    if glu is None:
+                        act = gu[:F] * torch.sigmoid(gu[:F]) * gu[F:]
+                    else:
+                        limit, alpha, shift = glu
+                        g, u = gu[:F].clamp(max=limit), gu[F:].clamp(-limit, limit)
+                        act = g * torch.sigmoid(alpha * g) * (u + shift)
+                    y = w_down[e].float() @ act.to(h.dtype).float()
                 else:
-                    y = x[t]
-                add_to[t] += weights[t, k] * y
+                    y = xin
+                add_to[t] += y if weight_inputs else weights[t, k] * y
 
     # ------------------------------------------------------------------ latent attention
     @staticmethod
@@ -408,13 +431,13 @@ class TorchKernels:
     def latent_prepare(self, z, q_rank, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, eps, cos, sin, slot_mapping, kc_pool, page_size, write=True):
         zf = z.float()
         dq, c, r = zf[:, :q_rank], zf[:, q_rank:q_rank + kv_rank], zf[:, q_rank + kv_rank:q_rank + kv_rank + rot_dim]
-        cq = dq * torch.rsqrt(dq.pow(2).mean(-1, keepdim=True) + eps) * q_norm.float()
+        cq = dq * torch.rsqrt(dq.pow(2).mean(-1, keepdim=True) + eps) * q_norm.float() if q_rank else None
         if write:
             c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * kv_norm.float()
             r = self._turn_pairs(r, cos, sin, rot_dims)
             page, off = (slot_mapping // page_size).long(), (slot_mapping % page_size).long()
             kc_pool[page, 0, off] = torch.cat([c, r], dim=-1).to(kc_pool.dtype)
-        return cq.to(z.dtype)
+        return cq.to(z.dtype) if q_rank else None
 
     def latent_absorb(self, q, w_uk, cos, sin, num_heads, head_dim, rot_dim, rot_dims, kv_rank):
         N = q.shape[0]
@@ -426,8 +449,43 @@ class TorchKernels:
     def latent_expand(self, o_lat, w_uv, gate, gate_col, num_heads, kv_rank, v_head_dim):
         N = o_lat.shape[0]
         o = torch.einsum("nhr,hrv->nhv", o_lat.float().view(N, num_heads, kv_rank), w_uv.float().view(num_heads, kv_rank, v_head_dim))
-        o = o.reshape(N, -1) * torch.sigmoid(gate[:, gate_col:gate_col + num_heads * v_head_dim].float())
+        o = o.reshape(N, -1)
+        if gate is not None:
+            o = o * torch.sigmoid(gate[:, gate_col:gate_col + num_heads * v_head_dim].float())
         return o.to(o_lat.dtype)
+
+    # ------------------------------------------------------------------ the matrix memory with exponential gates
+    def mlstm(self, z, q_col, k_col, v_col, gates, bias_i, bias_f, cap, num_heads, head_dim, v_head_dim, state, mstate, batch):
+        H, D, DV = num_heads, head_dim, v_head_dim
+        N = z.shape[0]
+        zf = z.float()
+        q = zf[:, q_col:q_col + H * D].view(N, H, D) * D ** -0.5
+        k = zf[:, k_col:k_col + H * D].view(N, H, D)
+        v = torch.cat([zf[:, v_col:v_col + H * DV].view(N, H, DV), torch.ones(N, H, 1)], dim=-1)   # the normaliser's column sees v = 1
+        xi, xf = gates[:, :H].float() + bias_i.float(), gates[:, H:2 * H].float() + bias_f.float()
+        if cap:
+            xi, xf = cap * torch.tanh(xi / cap), cap * torch.tanh(xf / cap)
+        lf = torch.nn.functional.logsigmoid(xf)
+        num, m_out = torch.zeros(N, H, DV + 1), torch.zeros(N, H)
+        for slot, s0, s1 in self._requests(batch):
+            S, m = state[slot].clone(), mstate[slot].clone()    # S [H, DV + 1, D]
+            for t in range(s0, s1):
+                m_new = torch.maximum(lf[t] + m, xi[t])
+                a, b = torch.exp(lf[t] + m - m_new), torch.exp(xi[t] - m_new)
+                S = a[:, None, None] * S + b[:, None, None] * v[t][:, :, None] * k[t][:, None, :]
+                m = m_new
+                num[t] = torch.einsum("hcd,hd->hc", S, q[t])
+                m_out[t] = m
+            state[slot], mstate[slot] = S, m
+        return num, m_out
+
+    def mlstm_finish(self, num, m, gate, gate_col, weight, eps, out_dtype):
+        N, H, DV = num.shape[0], num.shape[1], num.shape[2] - 1
+        den = torch.maximum(num[..., DV].abs(), torch.exp(-m)) + 1e-6
+        o = num[..., :DV] / den[..., None]
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+        o = o.reshape(N, H * DV) * weight.float() * torch.sigmoid(gate[:, gate_col:gate_col + H * DV].float())
+        return o.to(out_dtype)
 
     def argmax(self, logits):
         return logits.argmax(-1).to(torch.int32)
