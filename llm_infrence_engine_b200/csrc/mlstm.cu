@@ -65,9 +65,9 @@ template <int PARTS> __device__ __forceinline__ float parts_sum(float v) {
 
 // Block (x, h, r): COLS = ML_THREADS / PARTS columns of head h of request r, PARTS lanes to a column, each lane holding DPL entries of
 // it in registers (16-byte pieces, PARTS pieces apart). Rows of q and k come in tiles of ML_TILE tokens through a two-stage ring
-// (cp.async); a tile's gates are loaded into registers a tile ahead by the first warp, which turns them into (a, b, m) per token with
-// a scan over the tile (the step m -> max(f + m, i) composes: (f2, i2) after (f1, i1) is (f1 + f2, max(f2 + i1, i2))), so the
-// exponentials are taken once per token and block, not once per thread.
+// (cp.async); a tile's gates are loaded into registers a tile ahead by the first warp, which walks the chain of maxima over the tile
+// and turns the gates into (a, b, m) per token, a token per lane, so the exponentials are taken once per token and block, not once
+// per thread.
 template <typename T, int DMAX, int PARTS>
 __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const T* __restrict__ v, int v_stride, int v_col, const float* __restrict__ qf,
                                                                 const float* __restrict__ kf, const float* __restrict__ ig, const float* __restrict__ fg,
@@ -137,22 +137,23 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const T* __restr
     };
     auto store_small = [&](int buf) {
         if (threadIdx.x < 32) {
-            // inclusive scan of the step m -> max(F + m, I) over the tile's tokens, a token per lane
-            float F = pre_f, I = pre_i;
+            // the chain m -> max(f + m, i) over the tile's tokens, walked by every lane of the warp in the tokens' order (each step
+            // exactly as a token-by-token walk would take it, so the bits do not depend on where a tile begins); lane t keeps token t's
+            float m_run = m_carry, m_prev = m_carry, m_t = m_carry;
 #pragma unroll
-            for (int o = 1; o < ML_TILE; o <<= 1) {
-                const float pF = __shfl_up_sync(0xffffffffu, F, o), pI = __shfl_up_sync(0xffffffffu, I, o);
-                if ((int)threadIdx.x >= o) { I = fmaxf(F + pI, I); F = F + pF; }
+            for (int t = 0; t < ML_TILE; ++t) {
+                const float ft = __shfl_sync(0xffffffffu, pre_f, t), it = __shfl_sync(0xffffffffu, pre_i, t);
+                const float m_new = fmaxf(ft + m_run, it);
+                if ((int)threadIdx.x == t) { m_prev = m_run; m_t = m_new; }
+                m_run = m_new;
             }
-            const float m_t = fmaxf(F + m_carry, I);
-            float m_prev = __shfl_up_sync(0xffffffffu, m_t, 1);
-            if (threadIdx.x == 0) m_prev = m_carry;
+            if (threadIdx.x >= ML_TILE) m_t = m_run;
             if (threadIdx.x < ML_TILE) {
                 a_s[buf][threadIdx.x] = expf(pre_f + m_prev - m_t);
                 b_s[buf][threadIdx.x] = expf(pre_i - m_t);
                 m_s[buf][threadIdx.x] = m_t;
             }
-            m_carry = __shfl_sync(0xffffffffu, m_t, ML_TILE - 1);
+            m_carry = m_run;
         }
 #pragma unroll
         for (int n = 0; n < VPT; ++n) {
