@@ -20,7 +20,7 @@ batch of 8 requests and a context of 8192 tokens. A "step" is one decode step of
 ``roofline``  bytes a decode step must read (every weight once + the live requests' cache) / its time.
 ``points``    decode tokens per second at batch 1 and 64, same method as ``value``.
 
-``--workload serving | luvutar | zepalorn | mufotar`` measure other things (a stream of requests through the engine; the other architectures
+``--workload serving | luvutar | zepalorn | mufotar | memilorn`` measure other things (a stream of requests through the engine; the other architectures
 beside Qwen2 of equal size, Mufotar beside Zepalorn, with ``--kernels`` also kernel by kernel) and print lines of their own; the default line is
 unchanged by them.
 
@@ -1123,6 +1123,198 @@ def mufotar_workload(a) -> int:
     return 0
 
 
+# ``--workload memilorn``: the Memilorn decoder at layer sizes of real models, beside the Mufotar decoder (the closest of the
+# engine's other models: routed experts, a recurrence with a matrix state, softmax attention) of equal width, layer runs and experts.
+
+MEMILORN_SIZES = {
+    # name: (width, memory heads, memory key size, memory value size, attention heads, kv heads, head_dim, latent heads, latent head size,
+    #        latent rank, experts, chosen, expert ff, shared ff, vocab)
+    "1b-like": (1024, 8, 128, 128, 8, 2, 128, 8, 128, 256, 16, 4, 512, 768, 32768),
+    "3b-like": (2048, 16, 128, 128, 16, 4, 128, 16, 128, 512, 32, 4, 768, 2432, 32768),
+}
+MEMILORN_NAMES = ("width", "memory_heads", "memory_dim", "memory_vdim", "heads", "kv_heads", "head_dim", "latent_heads", "latent_head_dim", "kv_rank",
+                  "experts", "top", "expert_ff", "shared_ff", "vocab")
+
+
+def memilorn_config(size: str) -> dict:
+    """Five layers (attention whose heads talk, two matrix memories, latent attention, a matrix memory), of which the middle three run
+    twice: eight layer runs, every one with routed experts."""
+    W, mh, md, mv, H, G, d, lh, ld, rank, E, top, eff, sff, vocab = MEMILORN_SIZES[size]
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": E, "top": top}, "shared": {"ff": sff, "limit": 7.0}}
+    memory = {"type": "mlstm", "mixer": {"heads": mh, "dim": md, "vdim": mv, "gate_cap": 15.0}, "mlp": moe}
+    attention = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 30.0,
+                                                "rot": {"base": 100000.0, "dims": d}}, "mlp": moe}
+    latent = {"type": "latent_attention", "mixer": {"heads": lh, "dim": ld, "vdim": ld, "kv_rank": rank, "scale": ld ** -0.5}, "mlp": moe}
+    return {"architecture": "Memilorn", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "layers": [attention, memory, memory, latent, memory],
+            "loop": {"start": 1, "stop": 4, "times": 2}}
+
+
+def mufotar_beside_memilorn(size: str) -> dict:
+    """Mufotar with the same width and eight layers in the like places: the delta rule (a decay per head) where Memilorn has a matrix
+    memory, attention beside a selective scan where it has an attention, the same routed experts in every layer."""
+    W, mh, md, mv, H, G, d, lh, ld, rank, E, top, eff, sff, vocab = MEMILORN_SIZES[size]
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "identity": 0, "top": top}, "shared": {"ff": sff}}
+    delta = {"type": "delta", "mixer": {"heads": mh, "kv_heads": mh, "dim": md, "vdim": mv, "conv": 4}, "mlp": moe}
+    pair = {"type": "parallel", "mixer": {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": {"base": 100000.0, "dims": d}},
+                                          "right": {"inner": 2 * W, "state": 16, "dt_rank": W // 16, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}, "mlp": moe}
+    return {"architecture": "Mufotar", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "layers": [pair, delta, delta, pair, delta, delta, pair, delta]}
+
+
+def memilorn_kernel_points(torch, pk) -> dict:
+    """Memilorn's kernels one by one at the 3b-like layer sizes, each beside the kernel of the engine's other models that does the like
+    job at the same size: microseconds, and the fraction of its roofline (bytes that must move / copy peak, or flops / bf16 peak).
+    decode: 8 and 64 requests at 4,096 tokens bring one token each; prefill: one request brings 2,048."""
+    from types import SimpleNamespace
+
+    from llm_infrence_engine_b200.csrc import get_kernels
+
+    K = get_kernels()
+    W, mh, md, mv, H, G, d, lh, ld, rank, E, top, eff, sff, _ = MEMILORN_SIZES["3b-like"]
+    bf, dev = torch.bfloat16, "cuda"
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out = {}
+
+    def entry(us, bytes_=None, flops=None):
+        e = {"us": round(us, 2)}
+        if bytes_ is not None:
+            e["frac_of_copy_peak"] = round(bytes_ / (us * 1e-6) / hbm, 4)
+        if flops is not None:
+            e["frac_of_bf16_peak"] = round(flops / (us * 1e-6) / tf, 4)
+        return e
+
+    def batch_of(lens):
+        starts = [0]
+        for n in lens:
+            starts.append(starts[-1] + n)
+        return SimpleNamespace(seq_lens=list(lens), seq_starts_dev=torch.tensor(starts, dtype=torch.int32, device=dev), num_seqs=len(lens),
+                               seq_slots=torch.tensor(list(range(len(lens))), dtype=torch.int32, device=dev), max_seq_len=max(lens), _tables={})
+
+    def tables(batch, ctx, page=BLOCK):
+        per = -(-ctx // page)
+        t = torch.zeros((batch + 1, per), dtype=torch.int32, device=dev)
+        t[:batch] = (torch.randperm(batch * per, device=dev).to(torch.int32) + 1).view(batch, per)
+        return t, batch * per + 1
+
+    for what, batch, ctx, T in (("decode", 8, 4096, 1), ("decode_b64", 64, 4096, 1), ("prefill", 1, 2048, 2048)):
+        N = batch * T
+        b = batch_of([T] * batch)
+        # the recurrence: the matrix memory (scan, then division, norm and gate) beside the delta rule with a decay per head (scan, then
+        # norm and gate); both keep heads x key size x value size numbers per request
+        z = torch.randn(N, 2 * mh * md + 2 * mh * mv, device=dev).to(bf) * 0.5
+        gates = torch.randn(N, 2 * mh, device=dev)
+        zero, nw = torch.zeros(mh, device=dev), torch.ones(mh * mv, device=dev)
+        S, M = torch.zeros(batch + 1, mh, mv + 1, md, device=dev), torch.zeros(batch + 1, mh, device=dev)
+        moved = batch * 2 * 4 * mh * md * (mv + 1) + N * (2 * (2 * mh * md + mh * mv) + 2 * 4 * mh * (mv + 1))
+        out[f"matrix_memory_{what}_memilorn"] = entry(_time_graph(lambda: K.mlstm(z, 0, mh * md, 2 * mh * md, gates, zero, zero, 15.0, mh, md, mv, S, M, b), torch),
+                                                      moved, 6.0 * N * mh * md * (mv + 1))
+        num, mm = K.mlstm(z, 0, mh * md, 2 * mh * md, gates, zero, zero, 15.0, mh, md, mv, S, M, b)
+        out[f"memory_finish_{what}_memilorn"] = entry(_time_graph(lambda: K.mlstm_finish(num, mm, z, 2 * mh * md + mh * mv, nw, 1e-6, bf), torch), N * mh * mv * (4 + 2 + 2))
+        qkv = torch.randn(N, 2 * mh * md + mh * mv, device=dev).to(bf) * 0.5
+        zz = torch.randn(N, 2 * mh, device=dev).to(bf)
+        A_log, bias = torch.zeros(mh, device=dev), torch.full((mh,), -3.0, device=dev)
+        state = torch.zeros(batch + 1, mh, mv, md, device=dev)
+        moved = batch * 2 * 4 * mh * md * mv + N * (2 * (2 * mh * md + mh * mv) + 4 * mh * mv)
+        out[f"delta_rule_{what}_mufotar"] = entry(_time_graph(lambda: K.delta_rule(qkv, mh, mh, md, mv, zz[:, :mh], zz, mh, A_log, bias, state, b, decay_per_head=True), torch),
+                                                  moved, 8.0 * N * mh * md * mv)
+        o, g, nw1 = torch.randn(N, mh * mv, device=dev), torch.randn(N, mh * mv, device=dev).to(bf), torch.ones(mv, device=dev)
+        out[f"gated_norm_{what}_mufotar"] = entry(_time_graph(lambda: K.group_rmsnorm_gate(o, g, 0, nw1, mv, 1e-6, False, bf, gate_act="silu"), torch), N * mh * mv * (4 + 2 + 2))
+        # attention: heads that talk, with cap, sink and gate (Memilorn) beside plain grouped attention of the same sizes (Mufotar's left half)
+        table, pages = tables(batch, ctx)
+        seq = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(T)
+        pos = (torch.arange(T, dtype=torch.int32, device=dev) + (ctx - T)).repeat(batch)
+        kp, vp = torch.randn(pages, G, BLOCK, d, device=dev).to(bf), torch.randn(pages, G, BLOCK, d, device=dev).to(bf)
+        q, gt = torch.randn(N, H * d, device=dev).to(bf), torch.randn(N, H, device=dev).to(bf)
+        talk, sink = torch.eye(H, device=dev) + 0.05 * torch.randn(H, H, device=dev), torch.zeros(H, device=dev)
+        if T == 1:
+            moved, fl = batch * ctx * 2 * G * d * 2, None
+        else:
+            moved, fl = None, 4.0 * H * d * (T * (T + 1) / 2) * batch
+        out[f"attention_talk_{what}_memilorn"] = entry(_time_graph(lambda: (b._tables.clear(), K.attention_ext(q, 0, H, G, d, d, kp, vp, table, seq, pos, BLOCK, d ** -0.5, 0, ctx, batch=b,
+                                                                                                              softcap=30.0, talk=talk, sink=sink, gate=gt, gate_col=0, gate_per_head=True)), torch), moved, fl)
+        out[f"attention_{what}_mufotar"] = entry(_time_graph(lambda: (b._tables.clear(), K.attention_ext(q, 0, H, G, d, d, kp, vp, table, seq, pos, BLOCK, d ** -0.5, 0, ctx, batch=b)), torch), moved, fl)
+        del kp, vp
+        # latent attention: the attention over the cached latents, one key/value head whose values lie inside its keys (with a gate per head)
+        kc = torch.randn(pages, 1, BLOCK, rank, device=dev).to(bf)
+        ql = torch.randn(N, lh * rank, device=dev).to(bf)
+        if T == 1:
+            moved, fl = batch * ctx * rank * 2, None
+        else:
+            moved, fl = None, 4.0 * lh * rank * (T * (T + 1) / 2) * batch
+        out[f"attention_latent_{what}_memilorn"] = entry(_time_graph(lambda: (b._tables.clear(), K.attention_ext(ql, 0, lh, 1, rank, rank, kc, None, table, seq, pos, BLOCK, ld ** -0.5, 0, ctx, batch=b,
+                                                                                                                gate=gt, gate_col=0, gate_per_head=True)), torch), moved, fl)
+        del kc
+        # the feed-forward: sigmoid router, clamped experts with the weight on their input (Memilorn) beside softmax router, SiLU experts (Mufotar)
+        h = torch.randn(N, W, device=dev).to(bf)
+        w_router, corr = torch.randn(E, W, device=dev).to(bf) * 0.05, torch.zeros(E, device=dev)
+        wgu, wdn = torch.randn(E, 2 * eff, W, device=dev).to(bf) * 0.02, torch.randn(E, W, eff, device=dev).to(bf) * 0.02
+        y = torch.zeros(N, W, device=dev)
+        ids, wts = K.moe_router(h, w_router, None, top, scoring="sigmoid")
+        used = int(torch.unique(ids).numel())
+        fl = 6.0 * N * top * W * eff
+        moved = used * 3 * eff * W * 2 + N * W * (2 + 4)
+        out[f"router_{what}_memilorn"] = entry(_time_graph(lambda: K.moe_router(h, w_router, None, top, scoring="sigmoid"), torch), N * W * 2 + E * W * 2)
+        out[f"experts_{what}_memilorn"] = entry(_time_graph(lambda: K.moe_experts(h, ids, wts, wgu, wdn, add_to=y, glu=(7.0, 1.702, 1.0), weight_inputs=True), torch), moved, fl)
+        ids2, wts2 = K.moe_router(h, w_router, corr, top)
+        used2 = int(torch.unique(ids2).numel())
+        out[f"router_{what}_mufotar"] = entry(_time_graph(lambda: K.moe_router(h, w_router, corr, top), torch), N * W * 2 + E * W * 2)
+        out[f"experts_{what}_mufotar"] = entry(_time_graph(lambda: K.moe_experts(h, ids2, wts2, wgu, wdn, add_to=y), torch), used2 * 3 * eff * W * 2 + N * W * (2 + 4), fl)
+        del wgu, wdn
+    # the norm of a sublayer's input that also adds the scaled result of the sublayer before (Memilorn) beside the plain norm (Mufotar's has a bias)
+    N = 2048
+    res, w, bb, ls = torch.randn(N, W, device=dev), torch.ones(W, device=dev), torch.zeros(W, device=dev), torch.ones(W, device=dev)
+    delta = torch.randn(N, W, device=dev).to(bf)
+
+    def scaled_then_norm():
+        K._pending_post = (res, delta, ls, 0.0, True)
+        return K.layernorm(res, w, 1e-6, bf)
+
+    out["norm_with_layer_scale_memilorn"] = entry(_time_graph(scaled_then_norm, torch), N * W * (4 + 4 + 2 + 2))
+    out["layernorm_bias_mufotar"] = entry(_time_graph(lambda: K.layernorm(res, w, 1e-6, bf, bias=bb), torch), N * W * (4 + 2))
+    ids = torch.randint(0, 32768, (N,), device=dev, dtype=torch.int32)
+    table_e = torch.randn(32768, W, device=dev).to(bf)
+    out["embedding_added_again_memilorn"] = entry(_time_graph(lambda: K.embed_add(ids, table_e, res), torch), N * W * (2 + 4 + 4))
+    K.check_device_errors()
+    return out
+
+
+def memilorn_workload(a) -> int:
+    import torch
+
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    steps = min(a.steps, 256)
+    for size in MEMILORN_SIZES:
+        W, E, top, eff, vocab = (MEMILORN_SIZES[size][i] for i in (0, 10, 11, 12, 14))
+        row = {}
+        for name, config in (("memilorn", memilorn_config(size)), ("mufotar", mufotar_beside_memilorn(size))):
+            with tempfile.TemporaryDirectory() as tmp:
+                folder = write_random_model(config, Path(tmp) / "model", seed=0, store_dtype="bfloat16")
+                pt = model_points(folder, vocab, a.batch, a.context or 4096, a.prefill_tokens, steps, max(a.warmup, 3), torch)
+            # a step reads at most batch * top of a layer's experts: the others' matrices are taken off the bytes; a looped layer's weights
+            # are counted once per run (they are read again, from L2 or from memory)
+            runs = 8
+            own = len(config["layers"])
+            pt["decode_bytes"] -= own * max(0, E - a.batch * top) * 3 * eff * W * 2
+            pt["layer_runs"] = runs
+            pt["decode_frac_of_copy_peak"] = round(pt["decode_bytes"] / (pt["decode_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            row[name] = pt
+        sizes[size] = row
+    line = {"metric": f"Memilorn beside Mufotar of equal size: decode (batch {a.batch}, context {a.context or 4096}) and prefill ({a.prefill_tokens} tokens), bf16, random weights",
+            "unit": "ms and tokens/s per size", "n_gpus": 1, "impl": "ours", "dtype": "bf16", "steps": steps, "warmup": max(a.warmup, 3),
+            "data": "synthetic: random weights (seed 0), uniform random token ids, synthetic cache contents",
+            "config": {"sizes": {k: dict(zip(MEMILORN_NAMES, v)) for k, v in MEMILORN_SIZES.items()}, "block_size": BLOCK, "peaks": pk["source"],
+                       "l2": "weights + cache per step larger than L2, no flush"},
+            "clocks": sampler.stop(), "sizes": sizes}
+    if a.kernels:
+        line["kernels"] = memilorn_kernel_points(torch, pk)
+    print(json.dumps(line))
+    return 0
+
+
 def luvutar_workload(a) -> int:
     import torch
 
@@ -1170,11 +1362,12 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="measure one part only (for profiling); the JSON line then lacks the rest")
-    ap.add_argument("--workload", default="steps", choices=["steps", "serving", "luvutar", "zepalorn", "mufotar"],
+    ap.add_argument("--workload", default="steps", choices=["steps", "serving", "luvutar", "zepalorn", "mufotar", "memilorn"],
                     help="serving: continuous batching of --requests requests (prompts U[128,2048], outputs U[64,512]) through Engine; "
                          "luvutar, zepalorn: that decoder at two layer sizes beside the Qwen2 decoder of equal size (decode and prefill); "
-                         "mufotar: that decoder at two layer sizes beside the Zepalorn decoder of equal size")
-    ap.add_argument("--kernels", action="store_true", help="luvutar, zepalorn, mufotar: also time its kernels one by one beside their counterparts")
+                         "mufotar: that decoder at two layer sizes beside the Zepalorn decoder of equal size; "
+                         "memilorn: that decoder at two layer sizes beside the Mufotar decoder of equal size")
+    ap.add_argument("--kernels", action="store_true", help="luvutar, zepalorn, mufotar, memilorn: also time its kernels one by one beside their counterparts")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--token-budget", type=int, default=2048, help="serving: tokens per step (max_num_batched_tokens)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt")
@@ -1190,6 +1383,8 @@ def main() -> int:
         return zepalorn_workload(a)
     if a.workload == "mufotar":
         return mufotar_workload(a)
+    if a.workload == "memilorn":
+        return memilorn_workload(a)
     PREFILL_TOKENS = a.prefill_tokens
     shape_name, changes, shape_context = SHAPES[a.shape]
     MODEL.update(changes)

@@ -17,15 +17,24 @@ namespace {
 
 constexpr int TALK_THREADS = 256;
 constexpr int TALK_WARPS = TALK_THREADS / 32;
-constexpr int TALK_MAX_SLICE = 256;
+constexpr int TALK_MAX_SLICE = 128;   // (with 256 a decode step of 8 requests at 4,096 keys has fewer blocks than there are multiprocessors)
 constexpr int TALK_GC = 4;   // query heads of a group whose scores a lane forms from one pass over its key row
+constexpr int TALK_MAX_E = 16;   // output entries (head, dim) per thread that the staged form of the value product keeps in registers
+constexpr int TALK_V_CHUNK = 32;   // keys whose values are staged at a time, at most
+
+// floats (and integers) of the block's arrays before the staged values, rounded up to 16 bytes
+__host__ __device__ inline size_t talk_floats(int nq, int dk, int slice_keys) {
+    const int dkp = (dk + 3) & ~3;
+    const size_t n = (size_t)nq * dkp + (size_t)nq * nq + 2 * (size_t)nq * slice_keys + 2 * nq + slice_keys;
+    return (n + 3) & ~(size_t)3;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(TALK_THREADS) paged_attn_talk_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool, const int* __restrict__ block_table,
     int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions, const float* __restrict__ talk, T* __restrict__ out,
     float* __restrict__ part_acc, float* __restrict__ part_ml, int nq, int nkv, int dk, int dv, int page_size, float scale, int window,
-    int num_splits, int slice_keys, int vec_ok, attn_ext::Extras ex) {
+    int num_splits, int slice_keys, int vec_ok, int v_chunk, attn_ext::Extras ex) {
     extern __shared__ __align__(16) float talk_smem[];
     const int dkp = (dk + 3) & ~3;
     float* qs = talk_smem;                       // [nq][dkp]
@@ -75,6 +84,42 @@ __global__ void __launch_bounds__(TALK_THREADS) paged_attn_talk_kernel(
 
     // 1. capped scores of every head
     constexpr int VN = Vec16<T>::N;
+    if (v_chunk > 0 && vec_ok) {
+        // The keys of v_chunk positions at a time (all key/value heads) are brought into shared memory by 16-byte loads that run along
+        // the rows (a lane that walks its own row in the pages fetches 16 bytes of a 32-byte sector at a time, and the rows of a
+        // block's warps together do not stay in the first-level cache). There a lane owns a key and a warp the heads w, w + 8, ...:
+        // rows lie 16 bytes further apart than they are long, so that the lanes' pieces fall into different banks.
+        T* k_s = reinterpret_cast<T*>(talk_smem + talk_floats(nq, dk, slice_keys));
+        const int row_elems = nkv * dk + VN, per16 = dk / VN;
+        for (int c0 = 0; c0 < cnt; c0 += v_chunk) {
+            const int nk = min(v_chunk, cnt - c0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < nk * nkv * per16; i += TALK_THREADS) {
+                const int j = i / (nkv * per16), r = i % (nkv * per16);
+                const int kvh = r / per16, c = (r % per16) * VN;
+                *reinterpret_cast<uint4*>(k_s + (size_t)j * row_elems + kvh * dk + c) =
+                    *reinterpret_cast<const uint4*>(k_pool + (size_t)(rows[c0 + j] + kvh * page_size) * dk + c);
+            }
+            __syncthreads();
+            if (lane < nk) {
+                for (int h = warp; h < nq; h += TALK_WARPS) {
+                    const T* kr = k_s + (size_t)lane * row_elems + (h / G) * dk;
+                    const float* qh = qs + (size_t)h * dkp;
+                    float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
+                    for (int c = 0; c < dk; c += VN) {
+                        float kf[VN];
+                        Vec16<T>::load(kr + c, kf);
+#pragma unroll
+                        for (int i = 0; i < VN; i += 2) { s0 = fmaf(qh[c + i], kf[i], s0); s1 = fmaf(qh[c + i + 1], kf[i + 1], s1); }
+                    }
+                    const float sv = s0 + s1;
+                    sc[(size_t)h * slice_keys + c0 + lane] = ex.softcap > 0.f ? ex.softcap * tanhf(sv / ex.softcap) : sv;
+                }
+            }
+        }
+        __syncthreads();
+    } else {
     for (int base = warp * 32; base < cnt; base += TALK_WARPS * 32) {
         const int kl = base + lane;
         if (kl >= cnt) continue;
@@ -87,7 +132,8 @@ __global__ void __launch_bounds__(TALK_THREADS) paged_attn_talk_kernel(
 #pragma unroll
                 for (int g = 0; g < TALK_GC; ++g) s[g] = 0.f;
                 if (vec_ok) {
-                    for (int c = 0; c < dk; c += VN) {
+#pragma unroll 4
+                    for (int c = 0; c < dk; c += VN) {   // (unrolled: four pieces of the row are in flight)
                         float kf[VN];
                         Vec16<T>::load(kr + c, kf);
 #pragma unroll
@@ -115,6 +161,7 @@ __global__ void __launch_bounds__(TALK_THREADS) paged_attn_talk_kernel(
         }
     }
     __syncthreads();
+    }
 
     // 2. the heads' scores mixed; keys that the mask hides get -inf
     for (int kl = threadIdx.x; kl < cnt; kl += TALK_THREADS) {
@@ -153,7 +200,60 @@ __global__ void __launch_bounds__(TALK_THREADS) paged_attn_talk_kernel(
     // 4. weights times values, the keys in order
     const T* v_base = v_pool ? v_pool : k_pool;
     const int v_row = v_pool ? dv : dk;
-    for (int i = threadIdx.x; i < nq * dv; i += TALK_THREADS) {
+    if (v_chunk > 0) {
+        // The values of v_chunk keys at a time (all key/value heads) are brought into shared memory by 16-byte loads that run along the
+        // rows, then every thread adds up its entries (head, dim) from there: read straight from the pages, an entry's loads came one
+        // group of four after the other and a block waited on latency.
+        T* v_s = reinterpret_cast<T*>(talk_smem + talk_floats(nq, dk, slice_keys));
+        const int row_elems = nkv * dv, per16 = dv / VN;
+        const int E = (nq * dv + TALK_THREADS - 1) / TALK_THREADS;
+        float acc[TALK_MAX_E];
+#pragma unroll
+        for (int e = 0; e < TALK_MAX_E; ++e) acc[e] = 0.f;
+        for (int c0 = 0; c0 < cnt; c0 += v_chunk) {
+            const int nk = min(v_chunk, cnt - c0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < nk * nkv * per16; i += TALK_THREADS) {
+                const int j = i / (nkv * per16), r = i % (nkv * per16);
+                const int kvh = r / per16, c = (r % per16) * VN;
+                *reinterpret_cast<uint4*>(v_s + (size_t)(j * nkv + kvh) * dv + c) =
+                    *reinterpret_cast<const uint4*>(v_base + (size_t)(rows[c0 + j] + kvh * page_size) * v_row + c);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int e = 0; e < TALK_MAX_E; ++e) {
+                const int i = threadIdx.x + e * TALK_THREADS;
+                if (e < E && i < nq * dv) {
+                    const int h = i / dv, dim = i % dv;
+                    const float* w = sm + (size_t)h * slice_keys + c0;
+                    const T* vs = v_s + (size_t)(h / G) * dv + dim;
+                    float a = acc[e];
+                    for (int j = 0; j < nk; ++j) {
+                        const float wj = w[j];
+                        a = fmaf(wj, wj != 0.f ? to_f32(vs[(size_t)j * row_elems]) : 0.f, a);
+                    }
+                    acc[e] = a;
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < TALK_MAX_E; ++e) {
+            const int i = threadIdx.x + e * TALK_THREADS;
+            if (e < E && i < nq * dv) {
+                const int h = i / dv, dim = i % dv;
+                const float M = ml[2 * h], L = ml[2 * h + 1];
+                if (num_splits == 1) {
+                    out[((size_t)n * nq + h) * dv + dim] = from_f32<T>(attn_ext::finish<T>(acc[e], M, L, ex, h, dim, dv, gate_row));
+                } else {
+                    const size_t slot = ((size_t)n * nq + h) * num_splits + split;
+                    part_acc[slot * dv + dim] = acc[e];
+                    if (dim == 0) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
+                }
+            }
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < nq * dv; i += TALK_THREADS) {   // (sizes the staged form does not take: straight from the pages)
         const int h = i / dv, dim = i % dv;
         const int kvh = h / G;
         const float* w = sm + (size_t)h * slice_keys;
@@ -180,10 +280,7 @@ __global__ void __launch_bounds__(TALK_THREADS) paged_attn_talk_kernel(
     }
 }
 
-size_t talk_smem_bytes(int nq, int dk, int slice_keys) {
-    const int dkp = (dk + 3) & ~3;
-    return sizeof(float) * ((size_t)nq * dkp + (size_t)nq * nq + 2 * (size_t)nq * slice_keys + 2 * nq) + sizeof(int) * (size_t)slice_keys;
-}
+size_t talk_smem_bytes(int nq, int dk, int slice_keys) { return sizeof(float) * talk_floats(nq, dk, slice_keys); }
 
 template <typename T>
 int paged_attention_talk(const T* q, int q_stride, const T* k_pool, const T* v_pool, const int* block_table, int max_blocks, const int* token_seq,
@@ -194,16 +291,29 @@ int paged_attention_talk(const T* q, int q_stride, const T* k_pool, const T* v_p
         slice_keys > TALK_MAX_SLICE || slice_keys % 32 || (num_splits > 1 && !scratch) || (!v_pool && dv > dk) || (ex.gate_mode && !ex.gate) ||
         ex.rel || ex.temp_every)
         return LLMIE_ERR_BAD_ARGUMENT;
-    const size_t smem = talk_smem_bytes(nq, dk, slice_keys);
+    size_t smem = talk_smem_bytes(nq, dk, slice_keys);
     if (smem > 200 * 1024) return LLMIE_ERR_BAD_ARGUMENT;
     constexpr int VN = Vec16<T>::N;
     const int vec_ok = dk % VN == 0 && ((uintptr_t)k_pool % 16 == 0);
+    // the values go through shared memory where a chunk of at least 8 keys fits beside the scores, the rows are made of 16-byte pieces
+    // and a thread's entries fit its registers (sizes alone decide: a token's arithmetic is the same in every step)
+    int v_chunk = 0;
+    size_t per_key = 0;
+    const int v_row = v_pool ? dv : dk;
+    if (dv % VN == 0 && v_row % VN == 0 && ((uintptr_t)(v_pool ? v_pool : k_pool) % 16 == 0) && (long long)nq * dv <= (long long)TALK_MAX_E * TALK_THREADS) {
+        per_key = (size_t)nkv * dv * sizeof(T);
+        if (vec_ok && (size_t)(nkv * dk + VN) * sizeof(T) > per_key) per_key = (size_t)(nkv * dk + VN) * sizeof(T);   // (the keys' padded rows use the same room)
+        size_t fit = (160 * 1024 > smem ? 160 * 1024 - smem : 0) / per_key;
+        if (fit > (size_t)TALK_V_CHUNK) fit = TALK_V_CHUNK;
+        v_chunk = (int)(fit & ~(size_t)7);
+    }
+    smem += (size_t)v_chunk * per_key;
     if (smem > 48 * 1024) cudaFuncSetAttribute(paged_attn_talk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     float* part_acc = scratch;
     float* part_ml = scratch ? scratch + (size_t)N * nq * num_splits * dv : nullptr;
     paged_attn_talk_kernel<T><<<dim3(N, num_splits), TALK_THREADS, smem, s>>>(q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions,
                                                                                talk, out, part_acc, part_ml, nq, nkv, dk, dv, page_size, scale, window,
-                                                                               num_splits, slice_keys, vec_ok, ex);
+                                                                               num_splits, slice_keys, vec_ok, v_chunk, ex);
     int rc = launch_status();
     if (rc) return rc;
     if (num_splits > 1) {

@@ -63,39 +63,40 @@ template <int PARTS> __device__ __forceinline__ float parts_sum(float v) {
     return v;
 }
 
-// Block (x, h, r): COLS = ML_THREADS / PARTS columns of head h of request r, PARTS lanes to a column, each lane holding DPL entries of
-// it in registers (16-byte pieces, PARTS pieces apart). Rows of q and k come in tiles of ML_TILE tokens through a two-stage ring
+// Block (x, h, r): COLS columns of head h of request r, PARTS lanes to a group of CPL columns, each lane holding DPL entries of each
+// of them in registers (16-byte pieces, PARTS pieces apart). Rows of q and k come in tiles of ML_TILE tokens through a two-stage ring
 // (cp.async); a tile's gates are loaded into registers a tile ahead by the first warp, which walks the chain of maxima over the tile
 // and turns the gates into (a, b, m) per token, a token per lane, so the exponentials are taken once per token and block, not once
 // per thread.
-template <typename T, int DMAX, int PARTS>
+template <typename T, int DMAX, int PARTS, int CPL>
 __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const T* __restrict__ v, int v_stride, int v_col, const float* __restrict__ qf,
                                                                 const float* __restrict__ kf, const float* __restrict__ ig, const float* __restrict__ fg,
                                                                 float* __restrict__ state, float* __restrict__ mstate, const int* __restrict__ seq_starts,
                                                                 const int* __restrict__ seq_slots, float* __restrict__ num, float* __restrict__ m_out,
                                                                 int H, int D, int DV) {
-    constexpr int DPL = DMAX / PARTS, COLS = ML_THREADS / PARTS, Q = DMAX / 4;
+    constexpr int DPL = DMAX / PARTS, COLS = (ML_THREADS / PARTS) * CPL, Q = DMAX / 4;   // COLS: the block's columns, CPL to a group of lanes
     __shared__ __align__(16) float k_s[2][ML_TILE][DMAX];
     __shared__ __align__(16) float q_s[2][ML_TILE][DMAX];
     __shared__ float a_s[2][ML_TILE], b_s[2][ML_TILE], m_s[2][ML_TILE];
     __shared__ float v_s[2][ML_TILE][COLS];
     pdl_wait();
-    const int part = threadIdx.x % PARTS, my_col = threadIdx.x / PARTS;
+    const int part = threadIdx.x % PARTS, my_col = (threadIdx.x / PARTS) * CPL;   // the first of the lane group's CPL columns, within the block
     const int col = blockIdx.x * COLS + my_col;
     const int h = blockIdx.y, r = blockIdx.z;
     const int C = DV + 1;                 // the last column is the normaliser
-    const bool live = col < C;
     const bool vec = (D & 3) == 0;
     const int s0 = seq_starts[r], s1 = seq_starts[r + 1];
     const int slot = seq_slots[r];
-    float* st = state + (((size_t)slot * H + h) * C + (live ? col : 0)) * D;
-    float S[DPL];
+    float* st = state + ((size_t)slot * H + h) * C * D;
+    float S[CPL][DPL];
 #pragma unroll
-    for (int i = 0; i < DPL / 4; ++i) {
-        const int d = 4 * PARTS * i + 4 * part;
+    for (int u = 0; u < CPL; ++u)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) S[4 * i + c] = (live && d + c < D) ? st[d + c] : 0.f;
-    }
+        for (int i = 0; i < DPL / 4; ++i) {
+            const int d = 4 * PARTS * i + 4 * part;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) S[u][4 * i + c] = (col + u < C && d + c < D) ? st[(size_t)(col + u) * D + d + c] : 0.f;
+        }
     float m_carry = mstate[(size_t)slot * H + h];   // (every lane of the first warp keeps it)
 
     auto fetch = [&](int base, int buf) {
@@ -178,40 +179,64 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const T* __restr
         cp_commit();
         cp_wait<1>();
         __syncthreads();                       // this tile is in shared memory
+        // the tile's tokens in order; every token's partial sums stay in registers and the lanes of a column add them up for all
+        // tokens of the tile together (the shuffles of eight sums overlap instead of waiting for one another)
+        float rq[ML_TILE][CPL];
 #pragma unroll
         for (int t = 0; t < ML_TILE; ++t) {
-            if (t < count) {
-                const float a = a_s[buf][t];
-                const float bv = b_s[buf][t] * v_s[buf][t][my_col];
-                float r0 = 0.f, r1 = 0.f;
 #pragma unroll
-                for (int i = 0; i < DPL / 4; ++i) {
+            for (int u = 0; u < CPL; ++u) rq[t][u] = 0.f;
+            if (t < count) {
+                const float a = a_s[buf][t], b = b_s[buf][t];
+                float bv[CPL], r0[CPL], r1[CPL];
+#pragma unroll
+                for (int u = 0; u < CPL; ++u) { bv[u] = b * v_s[buf][t][my_col + u]; r0[u] = 0.f; r1[u] = 0.f; }
+#pragma unroll
+                for (int i = 0; i < DPL / 4; ++i) {   // a piece of k and of q serves all of the lane's columns
                     const float4 k4 = *reinterpret_cast<const float4*>(&k_s[buf][t][4 * PARTS * i + 4 * part]);
                     const float4 q4 = *reinterpret_cast<const float4*>(&q_s[buf][t][4 * PARTS * i + 4 * part]);
-                    float* s = S + 4 * i;
-                    s[0] = fmaf(bv, k4.x, a * s[0]); s[1] = fmaf(bv, k4.y, a * s[1]);
-                    s[2] = fmaf(bv, k4.z, a * s[2]); s[3] = fmaf(bv, k4.w, a * s[3]);
-                    r0 = fmaf(s[0], q4.x, r0); r1 = fmaf(s[1], q4.y, r1); r0 = fmaf(s[2], q4.z, r0); r1 = fmaf(s[3], q4.w, r1);
+#pragma unroll
+                    for (int u = 0; u < CPL; ++u) {
+                        float* s = S[u] + 4 * i;
+                        s[0] = fmaf(bv[u], k4.x, a * s[0]); s[1] = fmaf(bv[u], k4.y, a * s[1]);
+                        s[2] = fmaf(bv[u], k4.z, a * s[2]); s[3] = fmaf(bv[u], k4.w, a * s[3]);
+                        r0[u] = fmaf(s[0], q4.x, r0[u]); r1[u] = fmaf(s[1], q4.y, r1[u]); r0[u] = fmaf(s[2], q4.z, r0[u]); r1[u] = fmaf(s[3], q4.w, r1[u]);
+                    }
                 }
-                const float rq = parts_sum<PARTS>(r0 + r1);
-                if (live && part == 0) num[((size_t)(base + t) * H + h) * C + col] = rq;
+#pragma unroll
+                for (int u = 0; u < CPL; ++u) rq[t][u] = r0[u] + r1[u];
             }
         }
+#pragma unroll
+        for (int o = 1; o < PARTS; o <<= 1) {
+#pragma unroll
+            for (int t = 0; t < ML_TILE; ++t)
+#pragma unroll
+                for (int u = 0; u < CPL; ++u) rq[t][u] += __shfl_xor_sync(0xffffffffu, rq[t][u], o);
+        }
+        // every lane of the group holds all sums: lane t of the group stores token t's
+#pragma unroll
+        for (int t = 0; t < ML_TILE; ++t)
+            if (t < count && part == (t % PARTS)) {
+#pragma unroll
+                for (int u = 0; u < CPL; ++u)
+                    if (col + u < C) num[((size_t)(base + t) * H + h) * C + col + u] = rq[t][u];
+            }
         if (blockIdx.x == 0 && threadIdx.x < count) m_out[(size_t)(base + threadIdx.x) * H + h] = m_s[buf][threadIdx.x];
         if (more) store_small(buf ^ 1);
         __syncthreads();                       // everyone is done with this stage before it is filled again
     }
     cp_wait<0>();
     pdl_trigger();
-    if (live) {
+#pragma unroll
+    for (int u = 0; u < CPL; ++u)
 #pragma unroll
         for (int i = 0; i < DPL / 4; ++i) {
             const int d = 4 * PARTS * i + 4 * part;
 #pragma unroll
             for (int c = 0; c < 4; ++c)
-                if (d + c < D) st[d + c] = S[4 * i + c];
+                if (col + u < C && d + c < D) st[(size_t)(col + u) * D + d + c] = S[u][4 * i + c];
         }
-    }
     if (blockIdx.x == 0 && threadIdx.x == 0 && s0 < s1) mstate[(size_t)slot * H + h] = m_carry;
 }
 
@@ -235,25 +260,28 @@ __global__ void __launch_bounds__(128) mlstm_finish_kernel(const float* __restri
     }
 }
 
-template <typename T, int DM, int PARTS>
+template <typename T, int DM, int PARTS, int CPL>
 int launch_scan_as(const T* v, int v_stride, int v_col, const float* qf, const float* kf, const float* ig, const float* fg, float* state, float* mstate,
                    const int* seq_starts, const int* seq_slots, float* num, float* m_out, int H, int D, int DV, int R, cudaStream_t s) {
-    constexpr int COLS = ML_THREADS / PARTS;
+    constexpr int COLS = (ML_THREADS / PARTS) * CPL;
     const dim3 grid((DV + 1 + COLS - 1) / COLS, H, R);
-    return launch_kernel(mlstm_scan_kernel<T, DM, PARTS>, grid, dim3(ML_THREADS), 0, s, v, v_stride, v_col, qf, kf, ig, fg, state, mstate, seq_starts,
+    return launch_kernel(mlstm_scan_kernel<T, DM, PARTS, CPL>, grid, dim3(ML_THREADS), 0, s, v, v_stride, v_col, qf, kf, ig, fg, state, mstate, seq_starts,
                          seq_slots, num, m_out, H, D, DV);
 }
 
-// The lanes that share a column depend on the padded key size alone (a lane holds at least one 16-byte piece, at most 32 lanes).
+// The lanes that share a column depend on the padded key size alone (a lane holds one 16-byte piece of a short column, two from 64
+// entries on: fewer lanes to add up over), and a group of lanes owns up to four columns side by side, so that a piece of k and of q,
+// once fetched from shared memory, serves four columns: with one column to a group the kernel was bound by the instructions around the
+// multiply-adds (31 % of the issue slots busy, a quarter of the instructions multiply-adds; 1.54 ms at 128 entries and 2,048 tokens).
 template <typename T>
 int launch_scan(const T* v, int v_stride, int v_col, const float* qf, const float* kf, const float* ig, const float* fg, float* state, float* mstate,
                 const int* seq_starts, const int* seq_slots, float* num, float* m_out, int H, int D, int DV, int R, cudaStream_t s) {
 #define ML_ARGS v, v_stride, v_col, qf, kf, ig, fg, state, mstate, seq_starts, seq_slots, num, m_out, H, D, DV, R, s
-    if (D <= 16) return launch_scan_as<T, 16, 4>(ML_ARGS);
-    if (D <= 32) return launch_scan_as<T, 32, 8>(ML_ARGS);
-    if (D <= 64) return launch_scan_as<T, 64, 16>(ML_ARGS);
-    if (D <= 128) return launch_scan_as<T, 128, 32>(ML_ARGS);
-    return launch_scan_as<T, 256, 32>(ML_ARGS);
+    if (D <= 16) return launch_scan_as<T, 16, 4, 1>(ML_ARGS);
+    if (D <= 32) return launch_scan_as<T, 32, 8, 2>(ML_ARGS);
+    if (D <= 64) return launch_scan_as<T, 64, 8, 4>(ML_ARGS);
+    if (D <= 128) return launch_scan_as<T, 128, 16, 4>(ML_ARGS);
+    return launch_scan_as<T, 256, 32, 4>(ML_ARGS);
 #undef ML_ARGS
 }
 
