@@ -72,6 +72,7 @@ class CudaKernels:
         self.attention_ext_tile_rows = 32
         self.masked_attention_tensor_cores = True    # kept first tokens, chunks and soft caps on the tensor-core kernels too
         self.use_fa_attention_ext = True     # prompt portions with heads of 64 / 128: the kernel in which a warp owns 16 rows and all keys of a chunk
+        self.use_mma_attention_talk = True   # heads that talk, steps with prompt portions in bfloat16: plain scores and P V on the tensor cores
         self.head_matmul_library_rows = 64   # per-head products of latent attention: from this many rows on, one batched library product
         self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
@@ -111,7 +112,7 @@ class CudaKernels:
                    "llmie_selective_scan", "llmie_weighted_pair", "llmie_moe_route", "llmie_moe_sort", "llmie_moe_gemm", "llmie_moe_combine",
                    "llmie_moe_tile_rows", "llmie_moe_router", "llmie_moe_gather", "llmie_moe_grouped_tc", "llmie_moe_grouped_tc_rows",
                    "llmie_embed_add", "llmie_mlstm_prepare", "llmie_mlstm_scan", "llmie_mlstm_finish", "llmie_paged_attention_talk",
-                   "llmie_attention_talk_slice"):
+                   "llmie_attention_talk_slice", "llmie_attention_talk_mma_fits", "llmie_paged_attention_talk_mma"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = self._gate_up_glu_pair = None
@@ -1091,6 +1092,19 @@ class CudaKernels:
             raise KernelError("attention_ext: talking heads are not built together with a bias by distance or a query temperature")
         N = q.shape[0]
         esize = q.element_size()
+        per_tile = 0
+        if (self.use_mma_attention_talk and q.dtype == torch.bfloat16 and batch is not None and batch.max_seq_len > 1 and v_pool is not None
+                and not (window or keep_first or chunk) and gate_mode != 2 and (q_col * esize) % 16 == 0 and q.shape[1] % 8 == 0):
+            per_tile = self.lib.llmie_attention_talk_mma_fits(num_heads, num_kv_heads, head_dim, v_head_dim)
+        if per_tile:
+            # steps with prompt portions, bfloat16: a tile of 16 / (heads per key/value head) tokens and all heads on the tensor cores
+            tiles, tile_info = self._tiles(batch, per_tile, q.device)
+            self._check(self.lib.llmie_paged_attention_talk_mma(
+                ctypes.c_void_p(q.data_ptr() + q_col * esize), q.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+                _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, _ptr(talk), _ptr(out), num_heads, num_kv_heads, head_dim, v_head_dim,
+                page_size, ctypes.c_float(scale), _ptr(sink), ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize),
+                0 if gate is None else gate.shape[1], ctypes.c_float(softcap), self._stream()), "attention_ext (talking heads, tensor cores)")
+            return out
         slice_keys = self.lib.llmie_attention_talk_slice(num_heads, head_dim)
         if slice_keys < 32:
             raise KernelError(f"attention_ext: {num_heads} talking heads of {head_dim} entries do not fit the kernel's shared memory")

@@ -192,6 +192,16 @@ def test_attention_whose_heads_talk(K, dtype, nq, nkv, dk, dv, cap):
             got = K.attention_ext(q.cuda(), 8, nq, nkv, dk, dv, k_pool.cuda(), v_pool.cuda(), table.cuda(), seq.cuda(), pos.cuda(), page, 0.3, 0, ctx_len,
                                   batch=batch, softcap=cap, talk=talk.cuda(), **dkw)
             close(got, want, dtype, f"attention_ext {what} ({how})", scale=8.0 if dtype == "float32" else None)
+            if how == "portion" and dtype == "bfloat16":   # the tensor-core form took it where the sizes allow: the other form agrees
+                K.use_mma_attention_talk = False
+                try:
+                    other = K.attention_ext(q.cuda(), 8, nq, nkv, dk, dv, k_pool.cuda(), v_pool.cuda(), table.cuda(), seq.cuda(), pos.cuda(), page, 0.3, 0,
+                                            ctx_len, batch=batch, softcap=cap, talk=talk.cuda(), **dkw)
+                finally:
+                    K.use_mma_attention_talk = True
+                close(other, want, dtype, f"attention_ext {what} (portion, CUDA cores)")
+    fits = K.lib.llmie_attention_talk_mma_fits(nq, nkv, dk, dv)
+    assert (fits > 0) == ((nq, nkv, dk, dv) in {(8, 1, 128, 128), (16, 4, 64, 64), (2, 1, 48, 32)}) and fits in (0, 16 * nkv // nq)
     K.check_device_errors()
 
 
