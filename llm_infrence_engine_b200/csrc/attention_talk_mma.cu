@@ -4,7 +4,7 @@
 //
 //   1. keys and values of all key/value heads come into shared memory (cp.async along the rows, through the block table);
 //   2. every warp makes the plain scores of its rows (mma.sync m16n8k16, queries and keys by ldmatrix), scales and caps them in
-//      32-bit and leaves them in shared memory, laid out [token][key][head];
+//      32-bit and leaves them in shared memory, laid out [token][key][head] (padded against bank conflicts);
 //   3. every thread mixes the scores at its positions of the accumulator tile: score'_h = sum_g talk[h][g] score_g, 32-bit, on the
 //      CUDA cores (the mix is H multiply-adds per score whatever the form), masks them and takes them into its rows' running maximum
 //      and sum;
@@ -67,8 +67,12 @@ __global__ void __launch_bounds__(256) attn_talk_mma_kernel(const TalkParams P) 
     bf16* Qs = reinterpret_cast<bf16*>(tm_smem);                       // [nkv][16][ks]: row (token, head of the group) of key/value head kvh
     bf16* Ks = Qs + (size_t)nkv * 16 * ks;                             // [nkv][TM_KEYS][ks]
     bf16* Vs = Ks + (size_t)nkv * TM_KEYS * ks;                        // [nkv][TM_KEYS][vs]
-    float* sS = reinterpret_cast<float*>(Vs + (size_t)nkv * TM_KEYS * vs);   // [TT][TM_KEYS][nqp]: scaled and capped scores
-    float* tmx = sS + (size_t)TT * TM_KEYS * nqp;                      // [nq][nqp]: the mixing matrix
+    // [TT][TM_KEYS][nqp + 4] (+ 4 more per token): scaled and capped scores. A (token, key)'s heads lie 16 bytes further apart than they
+    // are long and a token's block 16 bytes further still, so that the 16-byte reads of a warp's positions (a quad's keys lie two apart,
+    // its rows one or more tokens apart) fall into different banks
+    float* sS = reinterpret_cast<float*>(Vs + (size_t)nkv * TM_KEYS * vs);
+    const int srow = nqp + 4, stok = TM_KEYS * srow + 4;
+    float* tmx = sS + (size_t)TT * stok;                               // [nq][nqp]: the mixing matrix
     int* rows_s = reinterpret_cast<int*>(tmx + (size_t)nq * nqp);      // [TM_KEYS]: where the chunk's keys lie in the pools
 
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;       // w: the warp's key/value head
@@ -88,7 +92,7 @@ __global__ void __launch_bounds__(256) attn_talk_mma_kernel(const TalkParams P) 
         const int h = i / nqp, g = i % nqp;
         tmx[i] = g < nq ? (P.talk ? P.talk[h * nq + g] : (h == g ? 1.f : 0.f)) : 0.f;
     }
-    for (int i = tid; i < TT * TM_KEYS * nqp; i += threads) sS[i] = 0.f;   // (the columns that pad a row of heads to 16 bytes stay zero)
+    for (int i = tid; i < TT * stok; i += threads) sS[i] = 0.f;   // (the columns that pad a row of heads to 16 bytes stay zero)
 
     // this thread's two rows of the warp's tile: (token, head)
     const int r0 = lane >> 2, r1 = r0 + 8, qd = lane & 3;
@@ -171,7 +175,7 @@ __global__ void __launch_bounds__(256) attn_talk_mma_kernel(const TalkParams P) 
                 const int t = i < 2 ? t0 : t1, h = i < 2 ? h0 : h1, key = j * 8 + 2 * qd + (i & 1);
                 float v = S[j][i] * P.scale;
                 if (P.ex.softcap > 0.f) v = P.ex.softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * v * inv_cap) + 1.0f));   // cap * tanh(v / cap), fast forms
-                if (t < TT) sS[((size_t)t * TM_KEYS + key) * nqp + h] = v;
+                if (t < TT) sS[(size_t)t * stok + key * srow + h] = v;
             }
         cp_wait_all();     // this chunk's values have landed
         place_rows(c0 + TM_KEYS);   // (this chunk's copies were all asked for before the loop came round)
@@ -188,7 +192,7 @@ __global__ void __launch_bounds__(256) attn_talk_mma_kernel(const TalkParams P) 
                 const int pos = i < 2 ? pos0 : pos1;
                 float v = -INFINITY;
                 if (c0 + key <= pos) {
-                    const float* src = sS + ((size_t)t * TM_KEYS + key) * nqp;
+                    const float* src = sS + (size_t)t * stok + key * srow;
                     const float* mr = tmx + (size_t)h * nqp;
                     float a = 0.f;
                     for (int g = 0; g < nqp; g += 4) {
@@ -261,7 +265,7 @@ __global__ void __launch_bounds__(256) attn_talk_mma_kernel(const TalkParams P) 
 size_t talk_mma_smem(int nq, int nkv, int dk, int dv) {
     const int Gs = nq / nkv, TT = 16 / Gs, nqp = (nq + 3) & ~3;
     return sizeof(bf16) * ((size_t)nkv * 16 * (dk + 8) + (size_t)nkv * TM_KEYS * (dk + 8) + (size_t)nkv * TM_KEYS * (dv + 8)) +
-           sizeof(float) * ((size_t)TT * TM_KEYS * nqp + (size_t)nq * nqp) + sizeof(int) * TM_KEYS;
+           sizeof(float) * ((size_t)TT * (TM_KEYS * (nqp + 4) + 4) + (size_t)nq * nqp) + sizeof(int) * TM_KEYS;
 }
 
 template <int NV>
